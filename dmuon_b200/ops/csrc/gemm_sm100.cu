@@ -1,0 +1,511 @@
+// Batched tcgen05 GEMM for sm_100a:  D = alpha * A * B^T + beta * C + diag * I.
+//
+// One persistent CTA per SM, 192 threads in three roles:
+//   warp 0      TMA producer: streams 128 x 64 (A) and BN x 64 (B) bf16/fp16
+//               tiles into a ring of 128-byte-swizzled shared-memory stages
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (128 x BN x 16) into
+//               one of two TMEM accumulators and commits mbarriers
+//   warps 2-5   epilogue: tcgen05.ld the finished accumulator, apply
+//               alpha/beta/diag, cast, store (and store the transposed tile
+//               for symmetric outputs) while the next tile's MMAs already run
+//
+// The tile list is data (a table built by the host), so the same kernel runs
+// dense products, lower-triangle-only symmetric products (Gram / SYRK) and any
+// batch of them.  Operands may be K-major or MN-major, so X X^T, X^T X, Q X and
+// X Q all run without a transposed copy of X.
+//
+// Covers the roles of the reference's symmetric-rank-k kernel
+// (dmuon/kernels/syrk_sm80.py:183-399, mma.sync + cp.async) and of the
+// library GEMMs its Newton-Schulz calls (dmuon/optim/newton_schulz.py:381-444).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <mutex>
+
+#include "gemm_sm100.cuh"
+#include "ptx_sm100.cuh"
+
+namespace dmuon {
+
+constexpr int BM = 128;
+constexpr int BK = 64;       // 64 two-byte elements = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 192;
+constexpr int kBlockBytes = 64 * 128;  // one 64 x 64 swizzled block (MN-major staging)
+
+template <int BN>
+struct Cfg {
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTmemCols = 2 * BN;
+  static constexpr int kBarBytes = 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;
+};
+
+struct KParams {
+  int M, N, K, batch;
+  const int4* tile_tab;
+  int tiles_per_batch;
+  int a_mn_major, b_mn_major, ab_fp16;
+  float alpha, beta, diag;
+  const void* C;
+  void* D;
+  void* D2;
+  const void* const* C_tab;
+  void* const* D_tab;
+  void* const* D2_tab;
+  long long ldc, ldd, ldd2;
+  long long strideC, strideD, strideD2;
+  int out_kind;
+  const int* b_ready;
+  int b_ready_epoch;
+  int* status;
+};
+
+// ---- epilogue helpers -------------------------------------------------------
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T x);
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half x) { return __half2float(x); }
+template <>
+__device__ __forceinline__ float to_f32<float>(float x) { return x; }
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float x);
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float x) { return __float2half_rn(x); }
+template <>
+__device__ __forceinline__ float from_f32<float>(float x) { return x; }
+
+template <typename T>
+__device__ __forceinline__ void load_row32(const T* src, float (&c)[32], int nvalid, bool vec) {
+  if (vec && nvalid == 32) {
+    constexpr int kPerVec = 16 / sizeof(T);
+    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+#pragma unroll
+    for (int i = 0; i < 32 / kPerVec; ++i) {
+      uint4 raw = s4[i];
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int j = 0; j < kPerVec; ++j) c[i * kPerVec + j] = to_f32<T>(e[j]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) c[j] = (j < nvalid) ? to_f32<T>(src[j]) : 0.f;
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void store_row32(T* dst, const float (&v)[32], int nvalid, bool vec) {
+  if (vec && nvalid == 32) {
+    constexpr int kPerVec = 16 / sizeof(T);
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+    for (int i = 0; i < 32 / kPerVec; ++i) {
+      uint4 raw;
+      T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+      for (int j = 0; j < kPerVec; ++j) e[j] = from_f32<T>(v[i * kPerVec + j]);
+      d4[i] = raw;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < nvalid) dst[j] = from_f32<T>(v[j]);
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void store_col32(T* dst, long long ld, const float (&v)[32], int nvalid) {
+  // dst points at element (col0, row) of the transposed tile; consecutive
+  // lanes hold consecutive rows, so each store instruction is contiguous
+  // across the warp.
+#pragma unroll
+  for (int j = 0; j < 32; ++j)
+    if (j < nvalid) dst[static_cast<long long>(j) * ld] = from_f32<T>(v[j]);
+}
+
+template <typename T>
+__device__ __forceinline__ void epilogue_chunk(const KParams& p, const T* Cb, T* Db,
+                                               __nv_bfloat16* D2b, float (&v)[32], int row, int col0,
+                                               bool mirror) {
+  const int nvalid = min(32, p.N - col0);
+  const bool row_ok = row < p.M;
+  if (p.beta != 0.f && row_ok) {
+    float c[32];
+    const T* src = Cb + static_cast<long long>(row) * p.ldc + col0;
+    const bool vec = ((p.ldc * sizeof(T)) % 16 == 0) && ((reinterpret_cast<uintptr_t>(Cb) & 15) == 0);
+    load_row32<T>(src, c, nvalid, vec);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = fmaf(p.beta, c[j], v[j]);
+  }
+  if (p.diag != 0.f) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j == row) v[j] += p.diag;
+  }
+  if (!row_ok) return;
+  {
+    T* dst = Db + static_cast<long long>(row) * p.ldd + col0;
+    const bool vec = ((p.ldd * sizeof(T)) % 16 == 0) && ((reinterpret_cast<uintptr_t>(Db) & 15) == 0);
+    store_row32<T>(dst, v, nvalid, vec);
+    if (mirror) store_col32<T>(Db + static_cast<long long>(col0) * p.ldd + row, p.ldd, v, nvalid);
+  }
+  if (D2b != nullptr) {
+    __nv_bfloat16* dst = D2b + static_cast<long long>(row) * p.ldd2 + col0;
+    const bool vec = ((p.ldd2 * 2) % 16 == 0) && ((reinterpret_cast<uintptr_t>(D2b) & 15) == 0);
+    store_row32<__nv_bfloat16>(dst, v, nvalid, vec);
+    if (mirror)
+      store_col32<__nv_bfloat16>(D2b + static_cast<long long>(col0) * p.ldd2 + row, p.ldd2, v, nvalid);
+  }
+}
+
+// ---- kernel -------------------------------------------------------------------
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const KParams p) {
+  using C = Cfg<BN>;
+  constexpr int S = C::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + S * C::kABytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * C::kStageBytes);
+  const uint32_t full0 = smem_u32(bars);
+  const uint32_t empty0 = smem_u32(bars + S);
+  const uint32_t tfull0 = smem_u32(bars + 2 * S);
+  const uint32_t tempty0 = smem_u32(bars + 2 * S + 2);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull0 + 8 * a, 1);
+      mbar_init(tempty0 + 8 * a, 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_tiles = p.tiles_per_batch * p.batch;
+  const int num_kb = (p.K + BK - 1) / BK;
+  int fail_code = 0;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- TMA producer ----------------
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+        const int b = t / p.tiles_per_batch;
+        const int4 e = p.tile_tab[t - b * p.tiles_per_batch];
+        const int m0 = e.x * BM;
+        const int n0 = e.y * BN;
+        if (p.b_ready != nullptr) {
+          if (!wait_flag_ge_gpu(p.b_ready + e.y, p.b_ready_epoch, kWaitBudgetCycles)) {
+            *abort_flag = 1;
+            fail_code = kStatusTimeoutPeerFlag;
+            break;
+          }
+        }
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(empty0 + 8 * stage, phase ^ 1u, abort_flag)) {
+            ok = false;
+            fail_code = kStatusTimeoutProducer;
+            break;
+          }
+          const uint32_t fb = full0 + 8 * stage;
+          mbar_arrive_expect_tx(fb, C::kStageBytes);
+          const uint32_t a_dst = smem_u32(sA + stage * C::kABytes);
+          const uint32_t b_dst = smem_u32(sB + stage * C::kBBytes);
+          if (!p.a_mn_major) {
+            tma_load_3d(a_dst, &tmA, fb, kb * BK, m0, b);
+          } else {
+#pragma unroll
+            for (int mb = 0; mb < BM / 64; ++mb)
+              tma_load_3d(a_dst + mb * kBlockBytes, &tmA, fb, m0 + 64 * mb, kb * BK, b);
+          }
+          if (!p.b_mn_major) {
+            tma_load_3d(b_dst, &tmB, fb, kb * BK, n0, b);
+          } else {
+#pragma unroll
+            for (int nb = 0; nb < BN / 64; ++nb)
+              tma_load_3d(b_dst + nb * kBlockBytes, &tmB, fb, n0 + 64 * nb, kb * BK, b);
+          }
+          if (++stage == S) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- MMA issuer ----------------
+      const uint32_t idesc =
+          make_idesc_f16(BM, BN, p.ab_fp16 != 0, p.a_mn_major != 0, p.b_mn_major != 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+        if (!mbar_wait_bounded(tempty0 + 8 * acc, acc_phase ^ 1u, abort_flag)) {
+          fail_code = kStatusTimeoutMma;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(full0 + 8 * stage, phase, abort_flag)) {
+            ok = false;
+            fail_code = kStatusTimeoutMma;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_base = smem_u32(sA + stage * C::kABytes);
+          const uint32_t b_base = smem_u32(sB + stage * C::kBBytes);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // K-major: 8-row groups are 1024 B apart, a K step of 16 elements is
+            // 32 B inside the swizzle row.  MN-major: 64-wide blocks are 8192 B
+            // apart, 8 K-rows are 1024 B apart, a K step of 16 rows is 2048 B.
+            const uint64_t adesc = p.a_mn_major
+                                       ? make_smem_desc_sw128(a_base + k * 2048, kBlockBytes, 1024)
+                                       : make_smem_desc_sw128(a_base + k * 32, 16, 1024);
+            const uint64_t bdesc = p.b_mn_major
+                                       ? make_smem_desc_sw128(b_base + k * 2048, kBlockBytes, 1024)
+                                       : make_smem_desc_sw128(b_base + k * 32, 16, 1024);
+            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty0 + 8 * stage);
+          if (++stage == S) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit(tfull0 + 8 * acc);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      const int b = t / p.tiles_per_batch;
+      const int4 e = p.tile_tab[t - b * p.tiles_per_batch];
+      const int m0 = e.x * BM;
+      const int n0 = e.y * BN;
+      const bool mirror = (e.z & 1) != 0;
+      if (!mbar_wait_bounded(tfull0 + 8 * acc, acc_phase, abort_flag)) {
+        fail_code = kStatusTimeoutEpilogue;
+        break;
+      }
+      tc_fence_after_sync();
+      const int row = m0 + q * 32 + lane;
+      const char* Cb = reinterpret_cast<const char*>(p.C_tab ? p.C_tab[b] : p.C);
+      char* Db = reinterpret_cast<char*>(p.D_tab ? p.D_tab[b] : p.D);
+      __nv_bfloat16* D2b = reinterpret_cast<__nv_bfloat16*>(p.D2_tab ? p.D2_tab[b] : p.D2);
+      const int esz = (p.out_kind == 2) ? 4 : 2;
+      if (!p.C_tab && Cb) Cb += static_cast<long long>(b) * p.strideC * esz;
+      if (!p.D_tab) Db += static_cast<long long>(b) * p.strideD * esz;
+      if (!p.D2_tab && D2b) D2b += static_cast<long long>(b) * p.strideD2;
+      for (int c = 0; c < BN; c += 32) {
+        const int col0 = n0 + c;
+        if (col0 >= p.N) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                          static_cast<uint32_t>(acc * BN + c),
+                      r);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = p.alpha * __uint_as_float(r[j]);
+        if (p.out_kind == 0) {
+          epilogue_chunk<__nv_bfloat16>(p, reinterpret_cast<const __nv_bfloat16*>(Cb),
+                                        reinterpret_cast<__nv_bfloat16*>(Db), D2b, v, row, col0, mirror);
+        } else if (p.out_kind == 1) {
+          epilogue_chunk<__half>(p, reinterpret_cast<const __half*>(Cb), reinterpret_cast<__half*>(Db),
+                                 D2b, v, row, col0, mirror);
+        } else {
+          epilogue_chunk<float>(p, reinterpret_cast<const float*>(Cb), reinterpret_cast<float*>(Db), D2b,
+                                v, row, col0, mirror);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    if (fail_code != 0 && p.status != nullptr) atomicCAS(p.status, 0, fail_code);
+    // Give bulk copies that may still be in flight time to land before the
+    // shared memory of this CTA is handed to another one.
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ---- host side ------------------------------------------------------------------
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                              CUtensorMapFloatOOBfill);
+
+static EncodeFn get_encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(sym);
+  });
+  return fn;
+}
+
+// Tensor map over a batched row-major matrix [batch][rows][cols] of 2-byte
+// elements; the box is box_cols x box_rows x 1 with 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, bool fp16, long long cols, long long rows,
+                    long long batch, long long ld, long long batch_stride, int box_cols, int box_rows) {
+  EncodeFn enc = get_encode_fn();
+  if (enc == nullptr) return -2;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows),
+                        static_cast<cuuint64_t>(batch)};
+  long long bs = (batch > 1 && batch_stride > 0) ? batch_stride : rows * ld;
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * 2, static_cast<cuuint64_t>(bs) * 2};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows), 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
+static std::atomic<long long> g_launches{0};
+
+template <int BN>
+static int launch(const DmuonGemmArgs& a, const CUtensorMap& tmA, const CUtensorMap& tmB,
+                  cudaStream_t stream, int num_sms) {
+  static bool attr_set[16] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  auto kern = gemm_tcgen05_kernel<BN>;
+  if (dev < 16 && !attr_set[dev]) {
+    cudaError_t e =
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::kSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set[dev] = true;
+  }
+  KParams p;
+  p.M = a.M; p.N = a.N; p.K = a.K; p.batch = a.batch;
+  p.tile_tab = reinterpret_cast<const int4*>(a.tile_tab);
+  p.tiles_per_batch = a.tiles_per_batch;
+  p.a_mn_major = a.a_mn_major; p.b_mn_major = a.b_mn_major; p.ab_fp16 = a.ab_fp16;
+  p.alpha = a.alpha; p.beta = a.beta; p.diag = a.diag;
+  p.C = a.C; p.D = a.D; p.D2 = a.D2;
+  p.C_tab = a.C_tab; p.D_tab = a.D_tab; p.D2_tab = a.D2_tab;
+  p.ldc = a.ldc; p.ldd = a.ldd; p.ldd2 = a.ldd2;
+  p.strideC = a.strideC; p.strideD = a.strideD; p.strideD2 = a.strideD2;
+  p.out_kind = a.out_kind;
+  p.b_ready = a.b_ready; p.b_ready_epoch = a.b_ready_epoch;
+  p.status = a.status;
+  if (p.C == nullptr && p.C_tab == nullptr) p.beta = 0.f;
+  const long long total = static_cast<long long>(a.tiles_per_batch) * a.batch;
+  int cap = (a.max_ctas > 0 && a.max_ctas < num_sms) ? a.max_ctas : num_sms;
+  int grid = static_cast<int>(total < cap ? total : cap);
+  if (grid <= 0) return 0;
+  kern<<<grid, kThreads, Cfg<BN>::kSmemBytes, stream>>>(tmA, tmB, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace dmuon
+
+extern "C" long long dmuon_launch_count(void) {
+  return dmuon::g_launches.load(std::memory_order_relaxed);
+}
+
+namespace dmuon {
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+}
+
+extern "C" int dmuon_gemm_sm100(const DmuonGemmArgs* args, void* stream_v) {
+  using namespace dmuon;
+  const DmuonGemmArgs& a = *args;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0 || a.batch <= 0) return 0;
+  if ((a.bn != 128 && a.bn != 256) || a.tile_tab == nullptr || a.tiles_per_batch <= 0) return -1;
+  if ((a.lda % 8) != 0 || (a.ldb % 8) != 0 || (a.strideA % 8) != 0 || (a.strideB % 8) != 0) return -1;
+  if ((reinterpret_cast<uintptr_t>(a.A) & 15) || (reinterpret_cast<uintptr_t>(a.B) & 15)) return -1;
+  static int num_sms[16] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 16 && num_sms[dev] == 0)
+    cudaDeviceGetAttribute(&num_sms[dev], cudaDevAttrMultiProcessorCount, dev);
+  const int sms = (dev < 16) ? num_sms[dev] : 148;
+
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!a.a_mn_major)
+    rc = make_map(&tmA, a.A, a.ab_fp16 != 0, a.K, a.M, a.batch, a.lda, a.strideA, BK, BM);
+  else
+    rc = make_map(&tmA, a.A, a.ab_fp16 != 0, a.M, a.K, a.batch, a.lda, a.strideA, 64, BK);
+  if (rc != 0) return rc;
+  if (!a.b_mn_major)
+    rc = make_map(&tmB, a.B, a.ab_fp16 != 0, a.K, a.N, a.batch, a.ldb, a.strideB, BK, a.bn);
+  else
+    rc = make_map(&tmB, a.B, a.ab_fp16 != 0, a.N, a.K, a.batch, a.ldb, a.strideB, 64, BK);
+  if (rc != 0) return rc;
+  if (a.bn == 256) return launch<256>(a, tmA, tmB, stream, sms);
+  return launch<128>(a, tmA, tmB, stream, sms);
+}

@@ -1,0 +1,265 @@
+"""Python front end of the tcgen05 GEMM kernel (``csrc/gemm_sm100.cu``).
+
+``gemm`` computes, for every matrix of a batch,
+
+    D = alpha * A @ B^T + beta * C + diag * I
+
+where ``A`` supplies ``M x K`` and ``B`` supplies ``N x K``.  Each operand is
+either stored K-major (``[M, K]`` row-major) or MN-major (``[K, M]``
+row-major), so the four products Newton-Schulz needs -- ``X X^T``, ``X^T X``,
+``Q X`` and ``X Q`` -- all run on the stored ``X`` without a transposed copy.
+With ``symmetric=True`` only tiles that touch the lower triangle are computed
+and strictly-lower tiles are also stored transposed, which halves the tensor
+work of Gram products (the reference's SYRK idea,
+dmuon/kernels/syrk_sm80.py:142-145, here on 128 x BN tcgen05 tiles).
+"""
+from __future__ import annotations
+
+import ctypes
+from functools import lru_cache
+
+import torch
+
+from . import build as _build
+
+BM = 128
+
+
+class _GemmArgs(ctypes.Structure):
+    _fields_ = [
+        ("A", ctypes.c_void_p),
+        ("B", ctypes.c_void_p),
+        ("lda", ctypes.c_longlong),
+        ("ldb", ctypes.c_longlong),
+        ("strideA", ctypes.c_longlong),
+        ("strideB", ctypes.c_longlong),
+        ("a_mn_major", ctypes.c_int),
+        ("b_mn_major", ctypes.c_int),
+        ("ab_fp16", ctypes.c_int),
+        ("M", ctypes.c_int),
+        ("N", ctypes.c_int),
+        ("K", ctypes.c_int),
+        ("batch", ctypes.c_int),
+        ("tile_tab", ctypes.c_void_p),
+        ("tiles_per_batch", ctypes.c_int),
+        ("bn", ctypes.c_int),
+        ("alpha", ctypes.c_float),
+        ("beta", ctypes.c_float),
+        ("diag", ctypes.c_float),
+        ("C", ctypes.c_void_p),
+        ("D", ctypes.c_void_p),
+        ("D2", ctypes.c_void_p),
+        ("C_tab", ctypes.c_void_p),
+        ("D_tab", ctypes.c_void_p),
+        ("D2_tab", ctypes.c_void_p),
+        ("ldc", ctypes.c_longlong),
+        ("ldd", ctypes.c_longlong),
+        ("ldd2", ctypes.c_longlong),
+        ("strideC", ctypes.c_longlong),
+        ("strideD", ctypes.c_longlong),
+        ("strideD2", ctypes.c_longlong),
+        ("out_kind", ctypes.c_int),
+        ("b_ready", ctypes.c_void_p),
+        ("b_ready_epoch", ctypes.c_int),
+        ("status", ctypes.c_void_p),
+        ("max_ctas", ctypes.c_int),
+    ]
+
+
+_OUT_KIND = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+
+_status_bufs: dict[int, torch.Tensor] = {}
+_tile_cache: dict[tuple, tuple[torch.Tensor, int]] = {}
+
+
+class KernelTimeout(RuntimeError):
+    """A bounded wait inside one of the kernels ran out (status word != 0)."""
+
+
+def status_buffer(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    buf = _status_bufs.get(idx)
+    if buf is None:
+        buf = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status_bufs[idx] = buf
+    return buf
+
+
+def check_status(device: torch.device | None = None) -> None:
+    """Synchronising read of the status word; raises if any kernel gave up."""
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    code = int(status_buffer(device)[0].item())
+    if code != 0:
+        status_buffer(device).zero_()
+        names = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue", 4: "peer/ready flag", 5: "bad argument"}
+        raise KernelTimeout(f"dmuon_b200 kernel wait ran out (code {code}: {names.get(code, '?')})")
+
+
+def symmetric_tiles(m: int, bn: int) -> list[tuple[int, int, int]]:
+    """Tiles (row_tile, col_tile, mirror) covering the lower triangle of m x m.
+
+    A tile is kept when any of its elements has row >= col; a tile whose
+    columns all lie strictly left of its rows is additionally stored
+    transposed.  Tiles that straddle the diagonal store what they compute.
+    """
+    out = []
+    mt = (m + BM - 1) // BM
+    for i in range(mt):
+        last_row = min(m, (i + 1) * BM) - 1
+        for j in range(last_row // bn + 1):
+            mirror = 1 if (j + 1) * bn <= i * BM else 0
+            out.append((i, j, mirror))
+    return out
+
+
+def dense_tiles(m: int, n: int, bn: int) -> list[tuple[int, int, int]]:
+    mt = (m + BM - 1) // BM
+    nt = (n + bn - 1) // bn
+    # column tile outermost: CTAs that run at the same time share B tiles in L2
+    return [(i, j, 0) for j in range(nt) for i in range(mt)]
+
+
+def tile_table(m: int, n: int, bn: int, symmetric: bool, device: torch.device) -> tuple[torch.Tensor, int]:
+    key = (m, n, bn, symmetric, device.index)
+    hit = _tile_cache.get(key)
+    if hit is None:
+        tiles = symmetric_tiles(m, bn) if symmetric else dense_tiles(m, n, bn)
+        flat = [[i, j, f, 0] for (i, j, f) in tiles]
+        tab = torch.tensor(flat, dtype=torch.int32).to(device)
+        hit = (tab, len(tiles))
+        _tile_cache[key] = hit
+    return hit
+
+
+@lru_cache(maxsize=None)
+def _fn():
+    lib = _build.load()
+    fn = lib.dmuon_gemm_sm100
+    fn.argtypes = [ctypes.POINTER(_GemmArgs), ctypes.c_void_p]
+    fn.restype = ctypes.c_int
+    return fn
+
+
+def pick_bn(m: int, n: int, batch: int, symmetric: bool) -> int:
+    """128-wide tiles when 256-wide ones would leave most SMs without a tile."""
+    if n <= 128:
+        return 128
+    t256 = len(symmetric_tiles(m, 256)) if symmetric else ((m + BM - 1) // BM) * ((n + 255) // 256)
+    return 256 if t256 * batch >= 148 else 128
+
+
+def gemm(
+    A: torch.Tensor,
+    B: torch.Tensor,
+    out: torch.Tensor,
+    *,
+    a_mn: bool = False,
+    b_mn: bool = False,
+    C: torch.Tensor | None = None,
+    alpha: float = 1.0,
+    beta: float = 0.0,
+    diag: float = 0.0,
+    symmetric: bool = False,
+    out2: torch.Tensor | None = None,
+    bn: int | None = None,
+    out_ptrs: torch.Tensor | None = None,
+    c_ptrs: torch.Tensor | None = None,
+    out2_ptrs: torch.Tensor | None = None,
+    out_ld: int | None = None,
+    out2_ld: int | None = None,
+    out_dtype: torch.dtype | None = None,
+    b_ready: torch.Tensor | None = None,
+    b_ready_epoch: int = 0,
+    max_ctas: int = 0,
+) -> torch.Tensor:
+    """Launch one batched product on the current CUDA stream.
+
+    ``A``/``B`` are 2-D or 3-D (leading batch) bf16 or fp16 tensors whose last
+    dimension is contiguous.  ``out`` (and ``C``) are bf16, fp16 or fp32 of the
+    same dtype.  When ``out_ptrs`` (an int64 device tensor with one address per
+    batch entry) is given, ``out`` may be ``None`` and each matrix is written to
+    its own allocation (same for ``c_ptrs`` / ``out2_ptrs``).
+    """
+    if A.dim() == 2:
+        A = A.unsqueeze(0)
+    if B.dim() == 2:
+        B = B.unsqueeze(0)
+    assert A.dtype == B.dtype and A.dtype in (torch.bfloat16, torch.float16)
+    assert A.stride(-1) == 1 and B.stride(-1) == 1
+    batch = A.shape[0]
+    assert B.shape[0] == batch
+    if a_mn:
+        K, M = A.shape[1], A.shape[2]
+    else:
+        M, K = A.shape[1], A.shape[2]
+    if b_mn:
+        Kb, N = B.shape[1], B.shape[2]
+    else:
+        N, Kb = B.shape[1], B.shape[2]
+    assert K == Kb, f"inner dimensions differ: {K} vs {Kb}"
+    if symmetric:
+        assert M == N
+    dev = A.device
+    if bn is None:
+        bn = pick_bn(M, N, batch, symmetric)
+    tab, ntiles = tile_table(M, N, bn, symmetric, dev)
+
+    args = _GemmArgs()
+    args.A = A.data_ptr()
+    args.B = B.data_ptr()
+    args.lda = A.stride(1)
+    args.ldb = B.stride(1)
+    args.strideA = A.stride(0) if batch > 1 else 0
+    args.strideB = B.stride(0) if batch > 1 else 0
+    args.a_mn_major = int(a_mn)
+    args.b_mn_major = int(b_mn)
+    args.ab_fp16 = int(A.dtype == torch.float16)
+    args.M, args.N, args.K, args.batch = M, N, K, batch
+    args.tile_tab = tab.data_ptr()
+    args.tiles_per_batch = ntiles
+    args.bn = bn
+    args.alpha, args.beta, args.diag = float(alpha), float(beta), float(diag)
+
+    if out is not None:
+        if out.dim() == 2:
+            out = out.unsqueeze(0)
+        assert out.stride(-1) == 1 and out.shape[-2:] == (M, N)
+        odt = out.dtype
+        args.D = out.data_ptr()
+        args.ldd = out.stride(1)
+        args.strideD = out.stride(0) if batch > 1 else 0
+    else:
+        assert out_ptrs is not None and out_ld is not None and out_dtype is not None
+        odt = out_dtype
+        args.D_tab = out_ptrs.data_ptr()
+        args.ldd = out_ld
+    args.out_kind = _OUT_KIND[odt]
+    if C is not None:
+        if C.dim() == 2:
+            C = C.unsqueeze(0)
+        assert C.dtype == odt and C.stride(-1) == 1
+        args.C = C.data_ptr()
+        args.ldc = C.stride(1)
+        args.strideC = C.stride(0) if batch > 1 else 0
+    elif c_ptrs is not None:
+        args.C_tab = c_ptrs.data_ptr()
+        args.ldc = args.ldd
+    if out2 is not None:
+        if out2.dim() == 2:
+            out2 = out2.unsqueeze(0)
+        assert out2.dtype == torch.bfloat16 and out2.stride(-1) == 1
+        args.D2 = out2.data_ptr()
+        args.ldd2 = out2.stride(1)
+        args.strideD2 = out2.stride(0) if batch > 1 else 0
+    elif out2_ptrs is not None:
+        args.D2_tab = out2_ptrs.data_ptr()
+        args.ldd2 = out2_ld if out2_ld is not None else args.ldd
+    if b_ready is not None:
+        args.b_ready = b_ready.data_ptr()
+        args.b_ready_epoch = int(b_ready_epoch)
+    args.status = status_buffer(dev).data_ptr()
+    args.max_ctas = int(max_ctas)
+    rc = _fn()(ctypes.byref(args), ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    if rc != 0:
+        raise RuntimeError(f"dmuon_gemm_sm100 failed with code {rc}")
+    return out

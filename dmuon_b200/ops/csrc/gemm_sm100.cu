@@ -53,6 +53,7 @@ struct KParams {
   int tiles_per_batch;
   int a_mn_major, b_mn_major, ab_fp16;
   float alpha, beta, diag;
+  const float* alpha_vec;
   const void* C;
   void* D;
   void* D2;
@@ -346,6 +347,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if (!p.C_tab && Cb) Cb += static_cast<long long>(b) * p.strideC * esz;
       if (!p.D_tab) Db += static_cast<long long>(b) * p.strideD * esz;
       if (!p.D2_tab && D2b) D2b += static_cast<long long>(b) * p.strideD2;
+      const float alpha = p.alpha_vec ? p.alpha * p.alpha_vec[b] : p.alpha;
       for (int c = 0; c < BN; c += 32) {
         const int col0 = n0 + c;
         if (col0 >= p.N) break;  // uniform across the warp
@@ -356,7 +358,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         tmem_ld_wait();
         float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = p.alpha * __uint_as_float(r[j]);
+        for (int j = 0; j < 32; ++j) v[j] = alpha * __uint_as_float(r[j]);
         if (p.out_kind == 0) {
           epilogue_chunk<__nv_bfloat16>(p, reinterpret_cast<const __nv_bfloat16*>(Cb),
                                         reinterpret_cast<__nv_bfloat16*>(Db), D2b, v, row, col0, mirror);
@@ -452,6 +454,7 @@ static int launch(const DmuonGemmArgs& a, const CUtensorMap& tmA, const CUtensor
   p.tiles_per_batch = a.tiles_per_batch;
   p.a_mn_major = a.a_mn_major; p.b_mn_major = a.b_mn_major; p.ab_fp16 = a.ab_fp16;
   p.alpha = a.alpha; p.beta = a.beta; p.diag = a.diag;
+  p.alpha_vec = a.alpha_vec;
   p.C = a.C; p.D = a.D; p.D2 = a.D2;
   p.C_tab = a.C_tab; p.D_tab = a.D_tab; p.D2_tab = a.D2_tab;
   p.ldc = a.ldc; p.ldd = a.ldd; p.ldd2 = a.ldd2;

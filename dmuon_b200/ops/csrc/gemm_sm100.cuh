@@ -28,6 +28,7 @@ struct DmuonGemmArgs {
   int bn;                      // 128 or 256
 
   float alpha, beta, diag;
+  const float* alpha_vec;      // optional per-batch device multiplier of alpha
   // Either flat base pointers with a batch stride, or per-batch pointer tables
   // (device arrays of `batch` pointers) when *_tab is not null.
   const void* C;

@@ -46,6 +46,7 @@ class _GemmArgs(ctypes.Structure):
         ("alpha", ctypes.c_float),
         ("beta", ctypes.c_float),
         ("diag", ctypes.c_float),
+        ("alpha_vec", ctypes.c_void_p),
         ("C", ctypes.c_void_p),
         ("D", ctypes.c_void_p),
         ("D2", ctypes.c_void_p),
@@ -168,6 +169,7 @@ def gemm(
     out_ld: int | None = None,
     out2_ld: int | None = None,
     out_dtype: torch.dtype | None = None,
+    alpha_vec: torch.Tensor | None = None,
     b_ready: torch.Tensor | None = None,
     b_ready_epoch: int = 0,
     max_ctas: int = 0,
@@ -254,6 +256,9 @@ def gemm(
     elif out2_ptrs is not None:
         args.D2_tab = out2_ptrs.data_ptr()
         args.ldd2 = out2_ld if out2_ld is not None else args.ldd
+    if alpha_vec is not None:
+        assert alpha_vec.dtype == torch.float32 and alpha_vec.numel() >= batch
+        args.alpha_vec = alpha_vec.data_ptr()
     if b_ready is not None:
         args.b_ready = b_ready.data_ptr()
         args.b_ready_epoch = int(b_ready_epoch)

@@ -1,0 +1,327 @@
+"""Batched Newton-Schulz and the fused Muon update on the sm_100a kernels.
+
+All matrices of one shape that a rank owns are stacked and pushed through the
+iteration together: every product below is ONE launch of the tcgen05 GEMM over
+the whole batch, so small Gram dimensions (1024, 256) still fill 148 SMs.
+
+Data flow for a batch of ``L`` matrices ``m0 x n0`` (natural orientation, no
+transposed copy is ever made):
+
+    prologue      mom = mu*mom + g ; u = g + mu*mom ; X = bf16(u) ; sumsq += u^2
+    scales        s = 1/(||u||_F + eps), s^2
+    gram          R = s^2 X X^T   (m0 <= n0)   or   s^2 X^T X   (m0 > n0)
+    per step      P = c R R + b R + a I ;  Q = P Q ;  R = (R P) P      symmetric
+    restart       X = s Q X  (or s X Q) ;  R = X X^T
+    final         W = (1 - lr wd) W - lr * scale * s * Q X   written straight
+                  into the fp32 master weights (and a bf16 publish copy)
+
+Symmetric products compute only the tiles that touch the lower triangle.
+Replaces the reference's per-matrix Python loop around SYRK / cuBLAS calls and
+its CUDA-graph cache (dmuon/optim/muon.py:1582-1747,
+dmuon/optim/newton_schulz.py:333-448, dmuon/optim/ns_graph.py:61-128).
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+
+from . import build as _build
+from . import gemm as G
+from . import multi_tensor as MT
+
+_avail: Optional[bool] = None
+
+
+def available() -> bool:
+    """True on a CUDA device of compute capability 10.x with the kernel
+    library present (built on demand when nvcc exists)."""
+    global _avail
+    if _avail is None:
+        ok = torch.cuda.is_available()
+        if ok:
+            major, _ = torch.cuda.get_device_capability()
+            ok = major == 10
+        if ok:
+            _build.load()   # raises when the library is missing: no silent fallback on a B200
+        _avail = ok
+    return _avail
+
+
+class _Workspace:
+    def __init__(self, L: int, m0: int, n0: int, dtype: torch.dtype, device):
+        self.key = (L, m0, n0, dtype)
+        m = min(m0, n0)
+        e = dict(device=device, dtype=dtype)
+        self.X = torch.empty(L, m0, n0, **e)
+        self.X2 = torch.empty(L, m0, n0, **e)
+        self.R = torch.empty(L, m, m, **e)
+        self.R2 = torch.empty(L, m, m, **e)
+        self.RP = torch.empty(L, m, m, **e)
+        self.P = torch.empty(L, m, m, **e)
+        self.Qa = torch.empty(L, m, m, **e)
+        self.Qb = torch.empty(L, m, m, **e)
+        self.sumsq = torch.zeros(L, device=device, dtype=torch.float32)
+        self.scale = torch.empty(L, device=device, dtype=torch.float32)
+        self.scale2 = torch.empty(L, device=device, dtype=torch.float32)
+        self.Xf32: Optional[torch.Tensor] = None
+
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in vars(self).values() if isinstance(t, torch.Tensor))
+
+
+_workspaces: dict[tuple, _Workspace] = {}
+_ptr_tables: dict[tuple, torch.Tensor] = {}
+MAX_WORKSPACE_BYTES = 6 << 30
+
+
+def workspace(L: int, m0: int, n0: int, dtype: torch.dtype, device) -> _Workspace:
+    key = (L, m0, n0, dtype, device.index)
+    ws = _workspaces.get(key)
+    if ws is None:
+        # keep at most one workspace per (shape, dtype): drop other batch sizes of this shape
+        for k in [k for k in _workspaces if k[1:] == key[1:]]:
+            del _workspaces[k]
+        ws = _Workspace(L, m0, n0, dtype, device)
+        _workspaces[key] = ws
+    return ws
+
+
+def release_workspaces() -> None:
+    _workspaces.clear()
+    _ptr_tables.clear()
+
+
+def max_batch(m0: int, n0: int, itemsize: int = 2) -> int:
+    """Largest batch whose workspace stays under ``MAX_WORKSPACE_BYTES``."""
+    m = min(m0, n0)
+    per = (2 * m0 * n0 + 6 * m * m) * itemsize
+    return max(1, MAX_WORKSPACE_BYTES // per)
+
+
+def _ptr_table(tensors: Sequence[torch.Tensor]) -> torch.Tensor:
+    key = tuple(t.data_ptr() for t in tensors)
+    tab = _ptr_tables.get(key)
+    if tab is None:
+        if len(_ptr_tables) > 4096:
+            _ptr_tables.clear()
+        tab = torch.tensor(key, dtype=torch.int64).to(tensors[0].device, non_blocking=True)
+        _ptr_tables[key] = tab
+    return tab
+
+
+def _gram(ws: _Workspace, X: torch.Tensor, out: torch.Tensor, left: bool, alpha_vec=None) -> None:
+    if left:
+        G.gemm(X, X, out, symmetric=True, alpha_vec=alpha_vec)
+    else:
+        G.gemm(X, X, out, a_mn=True, b_mn=True, symmetric=True, alpha_vec=alpha_vec)
+
+
+def _apply(Q: torch.Tensor, X: torch.Tensor, left: bool, **kw) -> None:
+    """``out = Q X`` (left) or ``X Q`` (right) with the epilogue given in kw."""
+    if left:
+        G.gemm(Q, X, kw.pop("out", None), b_mn=True, **kw)
+    else:
+        G.gemm(X, Q, kw.pop("out", None), **kw)
+
+
+def _iterate(ws: _Workspace, coefs, restarts, formulation: str, left: bool, x_is_raw: bool):
+    """Run all products but the final application.  Returns ``(Q, X, pending)``
+    where the result is ``Q X`` (times ``ws.scale`` when ``pending``)."""
+    X = ws.X
+    if formulation == "direct":
+        # X <- a X + (b A + c A A) X, A = X X^T ; X was normalised by the caller
+        Xn = ws.X2
+        for a, b, c in coefs:
+            _gram(ws, X, ws.R, left)
+            G.gemm(ws.R, ws.R, ws.P, C=ws.R, alpha=c, beta=b, symmetric=True)
+            _apply(ws.P, X, left, out=Xn, C=X, beta=a)
+            X, Xn = Xn, X
+        return None, X, False
+
+    pending = x_is_raw
+    _gram(ws, X, ws.R, left, alpha_vec=ws.scale2 if pending else None)
+    R, Rn = ws.R, ws.R2
+    pool = (ws.Qa, ws.Qb, ws.P)
+
+    def free(*busy):
+        return next(t for t in pool if all(t is not b for b in busy))
+
+    Q = None
+    last = len(coefs) - 1
+    for i, (a, b, c) in enumerate(coefs):
+        if i in restarts and i != 0:
+            Xn = ws.X2 if X is ws.X else ws.X
+            _apply(Q, X, left, out=Xn, alpha_vec=ws.scale if pending else None)
+            pending = False
+            X = Xn
+            _gram(ws, X, R, left)
+            Q = None
+        # step polynomial P = c R R + b R + a I
+        P = free(Q)
+        G.gemm(R, R, P, C=R, alpha=c, beta=b, diag=a, symmetric=True)
+        if Q is None:
+            Q = P                       # first step of a window: the factor IS the polynomial
+        else:
+            T = free(Q, P)
+            G.gemm(P, Q, T, symmetric=True)
+            Q = T
+        if i < last and (i + 1) not in restarts:
+            G.gemm(R, P, ws.RP, symmetric=True)
+            G.gemm(ws.RP, P, Rn, symmetric=True)
+            R, Rn = Rn, R
+    return Q, X, pending
+
+
+def _run(
+    ws: _Workspace,
+    coefs,
+    restarts,
+    formulation: str,
+    left: bool,
+    x_is_raw: bool,
+    final_kw: dict,
+) -> None:
+    Q, X, pending = _iterate(ws, coefs, restarts, formulation, left, x_is_raw)
+    if formulation == "direct":
+        # the iterate itself is the result: X is already orthogonalised
+        final_kw["copy_from"] = X
+        return
+    if pending:
+        final_kw["alpha_vec"] = ws.scale
+    _apply(Q, X, left, **final_kw)
+
+
+def newton_schulz_batched(
+    X_in: torch.Tensor,
+    coefs,
+    restarts,
+    eps: float = 1e-7,
+    formulation: str = "gram",
+    compute_dtype: Optional[torch.dtype] = None,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Orthogonalise every matrix of ``X_in`` ``[L, m0, n0]``; returns a tensor
+    of the input dtype."""
+    assert X_in.dim() == 3 and X_in.is_cuda
+    L, m0, n0 = X_in.shape
+    cd = compute_dtype or torch.bfloat16
+    if cd == torch.float32:
+        cd = torch.bfloat16
+    ws = workspace(L, m0, n0, cd, X_in.device)
+    left = m0 <= n0
+    Xf = X_in.float() if X_in.dtype != torch.float32 else X_in
+    sumsq = (Xf * Xf).sum(dim=(1, 2))
+    ws.scale.copy_(1.0 / (sumsq.sqrt() + eps))
+    ws.X.copy_(Xf * ws.scale.view(-1, 1, 1))
+    if out is None:
+        out = torch.empty(L, m0, n0, device=X_in.device, dtype=X_in.dtype)
+    odt = out.dtype
+    kw: dict = {}
+    if formulation == "direct":
+        _run(ws, coefs, restarts, formulation, left, False, kw)
+        out.copy_(kw["copy_from"])
+        return out
+    if odt in (torch.bfloat16, torch.float16, torch.float32):
+        kw["out"] = out
+        _run(ws, coefs, restarts, formulation, left, False, kw)
+        return out
+    raise TypeError(f"unsupported output dtype {odt}")
+
+
+def newton_schulz_single(G_in, coefs, restarts, eps, formulation, compute_dtype) -> torch.Tensor:
+    shape = G_in.shape
+    X = G_in.reshape(1, shape[0], -1)
+    if not X.is_contiguous():
+        X = X.contiguous()
+    return newton_schulz_batched(X, coefs, restarts, eps, formulation, compute_dtype).reshape(shape)
+
+
+def muon_update_batched(
+    grads: Sequence[torch.Tensor],
+    moms: Sequence[torch.Tensor],
+    masters: Optional[Sequence[torch.Tensor]],
+    *,
+    mu: float,
+    nesterov: bool,
+    coefs,
+    restarts,
+    formulation: str,
+    lr: float,
+    weight_decay: float,
+    update_scale: float,
+    eps: float = 1e-7,
+    compute_dtype: Optional[torch.dtype] = None,
+    publish: Optional[Sequence[torch.Tensor]] = None,
+    deltas: Optional[Sequence[torch.Tensor]] = None,
+    gscale: Optional[torch.Tensor] = None,
+) -> None:
+    """Momentum, Newton-Schulz and the weight update for ``L`` same-shape
+    matrices.
+
+    ``masters[i]`` (fp32, ``m0 x n0``) is updated in place:
+    ``W = (1 - lr*wd) W - lr*update_scale*NS(u)``; ``publish[i]`` (bf16) receives
+    a copy of the new weights.  With ``deltas`` instead of ``masters`` the
+    pre-scaled update ``-lr*update_scale*NS(u)`` is written there (fp32) and no
+    weight is touched (tensor-parallel owners scatter it).
+    """
+    L = len(grads)
+    if L == 0:
+        return
+    g0 = grads[0]
+    m0 = g0.shape[0]
+    n0 = g0.numel() // m0
+    dev = g0.device
+    cd = compute_dtype or torch.bfloat16
+    if cd == torch.float32:
+        cd = torch.bfloat16
+    ws = workspace(L, m0, n0, cd, dev)
+    left = m0 <= n0
+    ws.sumsq.zero_()
+    raw_ok = cd == torch.bfloat16 and formulation == "gram"
+    if raw_ok:
+        xs = [ws.X[i] for i in range(L)]
+        MT.muon_prologue(grads, moms, xs, list(range(L)), ws.sumsq, mu, nesterov, gscale)
+        MT.norm_scales(ws.sumsq, ws.scale, ws.scale2, eps)
+    else:
+        if ws.Xf32 is None:
+            ws.Xf32 = torch.empty(L, m0, n0, device=dev, dtype=torch.float32)
+        xs = [ws.Xf32[i] for i in range(L)]
+        MT.muon_prologue(grads, moms, xs, list(range(L)), ws.sumsq, mu, nesterov, gscale)
+        MT.norm_scales(ws.sumsq, ws.scale, ws.scale2, eps)
+        MT.cast(xs, [ws.X[i] for i in range(L)], scale=ws.scale, slots=list(range(L)))
+
+    step_alpha = -float(lr) * float(update_scale)
+    if formulation == "direct":
+        kw: dict = {}
+        _run(ws, coefs, restarts, formulation, left, False, kw)
+        O = kw["copy_from"]
+        with torch.no_grad():
+            for i in range(L):
+                if deltas is not None:
+                    deltas[i].copy_(O[i].view_as(deltas[i]).float() * step_alpha)
+                else:
+                    w = masters[i].view(m0, n0)
+                    if weight_decay:
+                        w.mul_(1.0 - lr * weight_decay)
+                    w.add_(O[i], alpha=step_alpha)
+                    if publish is not None and publish[i] is not None:
+                        publish[i].view(m0, n0).copy_(w)
+        return
+
+    if deltas is not None:
+        kw = dict(out_ptrs=_ptr_table(deltas), out_ld=n0, out_dtype=deltas[0].dtype, alpha=step_alpha)
+    else:
+        tab = _ptr_table(masters)
+        kw = dict(
+            out_ptrs=tab,
+            c_ptrs=tab,
+            out_ld=n0,
+            out_dtype=masters[0].dtype,
+            alpha=step_alpha,
+            beta=1.0 - float(lr) * float(weight_decay),
+        )
+        if publish is not None and all(p is not None for p in publish):
+            kw["out2_ptrs"] = _ptr_table(publish)
+            kw["out2_ld"] = n0
+    _run(ws, coefs, restarts, formulation, left, raw_ok, kw)

@@ -1,0 +1,601 @@
+"""Communication group: the dedicated parameters that share one hook boundary.
+
+A group owns the packed publish buffers (one per owner shard index: the owner
+writes its parameters into it, everybody else receives them) and drives the
+four data movements of a step:
+
+    publish   owner -> all, before forward (and again before backward when the
+              published copy is dropped after forward)
+    reduce    all -> owner, after backward; two stages on a replicate x shard
+              mesh (shard axis first, replicate axis second), mean over both
+    tp        gather of reduced shards to the tensor-parallel owner before the
+              matrix optimizer and scatter of the update afterwards
+    replicate post-step copy of the owner's master weights to the other
+              replicate rows
+
+All collectives run on the lanes of the shared context and are ordered with
+tickets; nothing here blocks the host.  Semantics follow the reference's
+``DedicatedParamGroup`` (dmuon/_backends/fsdp2/group.py:276-2177) and
+``DedicatedParamGroupDDP`` (dmuon/_backends/ddp/group.py:71-659); the layout
+differs: gradients are packed per owner before the reduce, so a layer issues
+one reduce per owner instead of one per parameter, and the owner's reduced
+gradient is a view of that packed buffer rather than a clone.
+"""
+from __future__ import annotations
+
+from collections import defaultdict
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+from torch.profiler import record_function
+
+from .comm import DedicatedCommContext, Lane, Ticket, mark_current
+from .dparam import DedicatedParam, alloc_storage, free_storage
+
+
+def _has_avg(group) -> bool:
+    try:
+        return dist.get_backend(group) == "nccl"
+    except Exception:
+        return False
+
+
+def reduce_mean(t: torch.Tensor, dst_global: int, group) -> None:
+    """Mean-reduce ``t`` onto ``dst_global``; other ranks' ``t`` is scratch."""
+    n = group.size()
+    if n == 1:
+        return
+    if _has_avg(group):
+        dist.reduce(t, dst=dst_global, op=dist.ReduceOp.AVG, group=group)
+    else:
+        dist.reduce(t, dst=dst_global, op=dist.ReduceOp.SUM, group=group)
+        if dist.get_rank() == dst_global:
+            t.div_(n)
+
+
+def all_reduce_mean(t: torch.Tensor, group) -> None:
+    n = group.size()
+    if n == 1:
+        return
+    if _has_avg(group):
+        dist.all_reduce(t, op=dist.ReduceOp.AVG, group=group)
+    else:
+        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
+        t.div_(n)
+
+
+class _PackedGrad:
+    """Packed gradient buffer of one owner coordinate during one reduce."""
+
+    __slots__ = ("coord", "params", "buf", "offsets")
+
+    def __init__(self, coord, params, buf, offsets):
+        self.coord, self.params, self.buf, self.offsets = coord, params, buf, offsets
+
+    def view_of(self, i: int) -> torch.Tensor:
+        p = self.params[i]
+        return self.buf[self.offsets[i] : self.offsets[i] + p.numel].view(p._orig_size)
+
+
+class DedicatedParamGroup:
+    mode = "fsdp"
+
+    def __init__(
+        self,
+        params: list[DedicatedParam],
+        module,
+        comm_ctx: DedicatedCommContext,
+        dp_group,
+        *,
+        reshard_after_forward: bool = True,
+        name: str = "",
+        delay_stage2_to_optimizer: bool = True,
+    ):
+        self.params = list(params)
+        self.module = module
+        self.comm_ctx = comm_ctx
+        self.dp_group = dp_group
+        self.replicate_group = comm_ctx.replicate_group
+        self.reshard_after_forward = bool(reshard_after_forward)
+        self.name = name or type(module).__name__
+        self.delay_stage2_to_optimizer = bool(delay_stage2_to_optimizer)
+        self.device = comm_ctx.device
+        self.shard_rank = dp_group.rank() if dp_group is not None else 0
+        self.shard_size = dp_group.size() if dp_group is not None else 1
+        self.replicate_rank = self.replicate_group.rank() if self.replicate_group is not None else 0
+        self.replicate_size = self.replicate_group.size() if self.replicate_group is not None else 1
+
+        self.bcast_params = [p for p in self.params if p._dmuon_route != "sharded_adamw"]
+        self.flat_params = [p for p in self.params if p._dmuon_route == "sharded_adamw"]
+        self.tp_params = [p for p in self.params if p.tp_group is not None]
+
+        self._is_unsharded = False
+        self._unshard_ticket: Optional[Ticket] = None
+        self._stage1_ticket: Optional[Ticket] = None
+        self._stage2_ticket: Optional[Ticket] = None
+        self._pending: list[_PackedGrad] = []
+        self._pending_flat: list[tuple[DedicatedParam, torch.Tensor]] = []
+        self._post_step_ticket: Optional[Ticket] = None
+        self._post_step_keep: list = []
+        self._tp_gather_ticket: Optional[Ticket] = None
+        self._tp_gather_keep: list = []
+        self._no_sync = False
+        self._post_forward_index: Optional[int] = None
+        self._backward_done = False
+        self._prefetched = False
+        self.next_forward_groups: list["DedicatedParamGroup"] = []
+
+        self._pub_by_shard: dict[int, list[DedicatedParam]] = defaultdict(list)
+        for p in self.bcast_params:
+            self._pub_by_shard[p.owner_shard].append(p)
+        self._packed: dict[int, torch.Tensor] = {}
+        if self.mode == "fsdp":
+            self._build_packed_buffers()
+
+    # ------------------------------------------------------------------ setup
+    def _param_dtype(self) -> torch.dtype:
+        return self.bcast_params[0]._param_dtype if self.bcast_params else torch.float32
+
+    def _build_packed_buffers(self) -> None:
+        """One persistent tensor per owner shard index; every parameter of that
+        owner becomes a view of it.  Storage is dropped right away and brought
+        back by ``unshard``."""
+        for s, plist in sorted(self._pub_by_shard.items()):
+            dtypes = {p._param_dtype for p in plist}
+            if len(dtypes) != 1:
+                raise ValueError(f"group {self.name}: parameters of owner shard {s} mix publish dtypes {dtypes}")
+            total = sum(p.numel for p in plist)
+            buf = torch.empty(total, dtype=plist[0]._param_dtype, device=self.device)
+            off = 0
+            for p in plist:
+                p.make_unsharded_param(buf[off : off + p.numel].view(p._orig_size))
+                p._packed_offset = off
+                off += p.numel
+            self._packed[s] = buf
+            free_storage(buf)
+        for p in self.flat_params:
+            per = p._flat_shard_numel
+            full = torch.empty(per * self.shard_size, dtype=p._param_dtype, device=self.device)
+            p._flat_full = full
+            p.make_unsharded_param(full[: p.numel].view(p._orig_size))
+            free_storage(full)
+
+    def _global_rank(self, group, local: int) -> int:
+        return dist.get_global_rank(group, local) if group is not None and dist.is_initialized() else 0
+
+    # ------------------------------------------------------------------ publish
+    def unshard(self, prefetch: bool = False) -> None:
+        if self.mode != "fsdp" or self._is_unsharded or self._unshard_ticket is not None:
+            if self._is_unsharded:
+                self.comm_ctx.count(self.name, "already_unsharded")
+            return
+        ctx = self.comm_ctx
+        lane = ctx.broadcast_lane
+        ctx.count(self.name, "prefetch_dispatch_calls" if prefetch else "demand_dispatch_calls")
+        # Storage is claimed on the current stream so that freeing it later (also
+        # on the current stream) is ordered after every consumer.
+        for buf in self._packed.values():
+            alloc_storage(buf)
+        for p in self.flat_params:
+            alloc_storage(p._flat_full)
+        lane.follow_current()
+        live = [p._unsharded_param for p in self.params]
+        with lane.use(), torch.no_grad(), torch.autograd._unsafe_preserve_version_counter(live):
+            with ctx.time_region("forward", self.name, "unshard", lane):
+                for s, plist in sorted(self._pub_by_shard.items()):
+                    buf = self._packed[s]
+                    if self.shard_rank == s:
+                        stale = [p for p in plist if not p._publish_fresh]
+                        if stale:
+                            dst = [buf[p._packed_offset : p._packed_offset + p.numel].view(p._orig_size) for p in stale]
+                            torch._foreach_copy_(dst, [p._owned_data for p in stale])
+                        for p in plist:
+                            p._publish_fresh = False
+                    if self.shard_size > 1:
+                        nbytes = buf.numel() * buf.element_size()
+                        with record_function(
+                            f"dmuon.unshard_broadcast.owner{s}.bytes{nbytes}.params{len(plist)}.{self.name}"
+                        ):
+                            dist.broadcast(buf, src=self._global_rank(self.dp_group, s), group=self.dp_group)
+                        ctx.count(self.name, "owner_broadcast_bytes", nbytes)
+                for p in self.flat_params:
+                    self._all_gather_flat(p)
+        self._unshard_ticket = lane.mark()
+        self._prefetched = prefetch
+
+    def _all_gather_flat(self, p: DedicatedParam) -> None:
+        shard = p._sharded_adamw_data.to(p._param_dtype)
+        if self.shard_size > 1:
+            dist.all_gather_into_tensor(p._flat_full, shard, group=self.dp_group)
+        else:
+            p._flat_full.copy_(shard)
+
+    def wait_for_unshard(self) -> None:
+        if self.mode != "fsdp":
+            return
+        if self._unshard_ticket is not None:
+            self._unshard_ticket.wait_on_current()
+            self._unshard_ticket = None
+            self.comm_ctx.count(self.name, "wait_calls")
+        if not self._is_unsharded:
+            for p in self.params:
+                p.attach_to_modules()
+                p._is_unsharded = True
+            self._is_unsharded = True
+
+    def reshard(self) -> None:
+        if self.mode != "fsdp" or not (self._is_unsharded or self._unshard_ticket is not None):
+            return
+        if self._unshard_ticket is not None:
+            # a prefetch nobody consumed: order the free after the transfer
+            self._unshard_ticket.wait_on_current()
+            self._unshard_ticket = None
+        for p in self.params:
+            p.detach_from_modules()
+            p._is_unsharded = False
+        for buf in self._packed.values():
+            free_storage(buf)
+        for p in self.flat_params:
+            free_storage(p._flat_full)
+        self._is_unsharded = False
+
+    # ------------------------------------------------------------------ reduce
+    def _grad_dtype_of(self, p: DedicatedParam, g: torch.Tensor) -> torch.dtype:
+        return p._grad_dtype or g.dtype
+
+    def reduce_grads(self) -> None:
+        """Pack this backward's gradients per owner and start the mean-reduce."""
+        ctx = self.comm_ctx
+        with_grad = [(p, p.local_grad()) for p in self.params]
+        with_grad = [(p, g) for p, g in with_grad if g is not None]
+        if not with_grad:
+            return
+        if self._no_sync:
+            with torch.no_grad():
+                for p, g in with_grad:
+                    if p._accumulated_grad is None:
+                        p._accumulated_grad = g.detach().clone()
+                    else:
+                        p._accumulated_grad.add_(g)
+                    p.clear_local_grad()
+            return
+        if self._pending or self._pending_flat:
+            # an earlier backward of this accumulation window is still in flight
+            self.wait_for_reduce()
+
+        by_coord: dict[tuple, list] = defaultdict(list)
+        flats = []
+        for p, g in with_grad:
+            if p._dmuon_route == "sharded_adamw":
+                flats.append((p, g))
+            else:
+                by_coord[p.owner_rank].append((p, g))
+
+        packs: list[_PackedGrad] = []
+        with torch.no_grad():
+            for coord in sorted(by_coord):
+                items = by_coord[coord]
+                dtype = self._grad_dtype_of(*items[0])
+                total = sum(p.numel for p, _ in items)
+                buf = torch.empty(total, dtype=dtype, device=self.device)
+                offs, off = [], 0
+                for p, _ in items:
+                    offs.append(off)
+                    off += p.numel
+                pack = _PackedGrad(coord, [p for p, _ in items], buf, offs)
+                views = [pack.view_of(i) for i in range(len(items))]
+                torch._foreach_copy_(views, [g for _, g in items])
+                acc = [(v, p._accumulated_grad) for v, (p, _) in zip(views, items) if p._accumulated_grad is not None]
+                if acc:
+                    torch._foreach_add_([v for v, _ in acc], [a.to(dtype) for _, a in acc])
+                for p, _ in items:
+                    p._accumulated_grad = None
+                    p.clear_local_grad()
+                packs.append(pack)
+            flat_bufs = []
+            for p, g in flats:
+                per = p._flat_shard_numel
+                dtype = self._grad_dtype_of(p, g)
+                padded = torch.zeros(per * self.shard_size, dtype=dtype, device=self.device)
+                padded[: p.numel].copy_(g.reshape(-1))
+                if p._accumulated_grad is not None:
+                    padded[: p.numel].add_(p._accumulated_grad.reshape(-1).to(dtype))
+                    p._accumulated_grad = None
+                p.clear_local_grad()
+                flat_bufs.append((p, padded))
+
+        lane = ctx.reduce_lane
+        lane.follow_current()
+        with lane.use(), torch.no_grad():
+            with record_function(f"dmuon.reduce_grads.stage1.{self.name}"):
+                for pack in packs:
+                    lane.keep_alive(pack.buf)
+                    if self.shard_size > 1:
+                        reduce_mean(pack.buf, self._global_rank(self.dp_group, pack.coord[0]), self.dp_group)
+                for p, padded in flat_bufs:
+                    lane.keep_alive(padded)
+                    out = torch.empty(p._flat_shard_numel, dtype=padded.dtype, device=self.device)
+                    lane.keep_alive(out)
+                    if self.shard_size > 1:
+                        dist.reduce_scatter_tensor(out, padded, op=dist.ReduceOp.SUM, group=self.dp_group)
+                        out.div_(self.shard_size)
+                    else:
+                        out.copy_(padded)
+                    self._pending_flat.append((p, out))
+        self._stage1_ticket = lane.mark()
+        self._pending = packs
+        ctx.last_reduced_group = self
+        if self.replicate_size > 1:
+            self._launch_stage2()
+
+    def _launch_stage2(self) -> None:
+        """Replicate-axis mean of what stage 1 left on the owner's shard column."""
+        ctx = self.comm_ctx
+        lane = ctx.replicate_reduce_lane
+        if self._stage1_ticket is not None:
+            self._stage1_ticket.wait_on(lane)
+        with lane.use(), torch.no_grad():
+            with record_function(f"dmuon.reduce_grads.stage2.{self.name}"):
+                for pack in self._pending:
+                    s, r = pack.coord
+                    if self.shard_rank != s:
+                        continue
+                    lane.keep_alive(pack.buf)
+                    reduce_mean(pack.buf, self._global_rank(self.replicate_group, r), self.replicate_group)
+                for _, out in self._pending_flat:
+                    lane.keep_alive(out)
+                    all_reduce_mean(out, self.replicate_group)
+        self._stage2_ticket = lane.mark()
+
+    def wait_for_stage1_reduce(self) -> None:
+        if self._stage1_ticket is not None:
+            self._stage1_ticket.wait_on_current()
+
+    def wait_for_reduce(self, lane: Optional[Lane] = None) -> None:
+        """Make the reduced gradients visible as ``_reduced_grad`` on the owner
+        (ordered on ``lane`` or, by default, the current stream)."""
+        for t in (self._stage1_ticket, self._stage2_ticket):
+            if t is None:
+                continue
+            if lane is not None:
+                t.wait_on(lane)
+            else:
+                t.wait_on_current()
+        self._stage1_ticket = self._stage2_ticket = None
+        scope = lane.use() if lane is not None else torch.no_grad()
+        with scope, torch.no_grad():
+            for pack in self._pending:
+                s, r = pack.coord
+                mine = self.shard_rank == s and self.replicate_rank == r
+                if not mine:
+                    continue
+                for i, p in enumerate(pack.params):
+                    v = pack.view_of(i)
+                    if p._reduced_grad is None:
+                        p._reduced_grad = v
+                    else:
+                        p._reduced_grad = p._reduced_grad + v.to(p._reduced_grad.dtype)
+            for p, out in self._pending_flat:
+                if p._sharded_adamw_grad is None:
+                    p._sharded_adamw_grad = out
+                else:
+                    p._sharded_adamw_grad = p._sharded_adamw_grad + out
+        self._pending = []
+        self._pending_flat = []
+        if self.comm_ctx.last_reduced_group is self:
+            self.comm_ctx.last_reduced_group = None
+
+    def has_pending_reduce(self) -> bool:
+        return bool(self._pending or self._pending_flat)
+
+    # ------------------------------------------------------------------ tensor parallel
+    def tp_gather_grads(self, lane: Optional[Lane] = None) -> None:
+        """Collect the reduced shards of every TP-sharded parameter on its TP
+        owner.  Every TP peer of a DP owner takes part, in parameter order."""
+        todo = [p for p in self.tp_params if p.is_owner and p._reduced_grad is not None]
+        if not todo:
+            return
+        lane = lane or self.comm_ctx.reduce_lane
+        lane.follow_current()
+        keep = []
+        with lane.use(), torch.no_grad():
+            with record_function(f"dmuon.tp_gather.{self.name}"):
+                for p in todo:
+                    g = p._reduced_grad.contiguous()
+                    lane.keep_alive(g)
+                    tsize = p.tp_group.size()
+                    if p.is_tp_owner:
+                        parts = [torch.empty_like(g) for _ in range(tsize)]
+                        for t in parts:
+                            lane.keep_alive(t)
+                        dist.gather(g, gather_list=parts, dst=p._tp_owner_global_rank, group=p.tp_group)
+                        keep.append((p, parts))
+                    else:
+                        dist.gather(g, gather_list=None, dst=p._tp_owner_global_rank, group=p.tp_group)
+        self._tp_gather_keep = keep
+        self._tp_gather_ticket = lane.mark()
+
+    def materialize_tp_grads(self) -> None:
+        if self._tp_gather_ticket is not None:
+            self._tp_gather_ticket.wait_on_current()
+            self._tp_gather_ticket = None
+        for p, parts in self._tp_gather_keep:
+            p._tp_full_grad = torch.cat(parts, dim=p.shard_dim)
+        self._tp_gather_keep = []
+
+    def tp_scatter_delta(self, lane: Optional[Lane] = None) -> Optional[Ticket]:
+        """Send every TP peer its slice of the owner's pre-scaled update and
+        apply ``w = w * wd_factor + slice`` to the master shard."""
+        todo = [p for p in self.tp_params if p.is_owner and (p._reduced_grad is not None or p._tp_full_delta is not None)]
+        if not todo:
+            return None
+        lane = lane or self.comm_ctx.replicate_broadcast_lane
+        lane.follow_current()
+        lane.follow(self.comm_ctx.reduce_lane)      # gather and scatter share the TP communicator
+        with lane.use(), torch.no_grad():
+            with record_function(f"dmuon.tp_scatter.{self.name}"):
+                for p in todo:
+                    recv = torch.empty(p._orig_size, dtype=p._owned_data.dtype, device=self.device)
+                    lane.keep_alive(recv)
+                    if p.is_tp_owner:
+                        delta = p._tp_full_delta.to(p._owned_data.dtype)
+                        pieces = [c.contiguous() for c in delta.chunk(p.tp_group.size(), dim=p.shard_dim)]
+                        for c in pieces:
+                            lane.keep_alive(c)
+                        dist.scatter(recv, scatter_list=pieces, src=p._tp_owner_global_rank, group=p.tp_group)
+                    else:
+                        dist.scatter(recv, scatter_list=None, src=p._tp_owner_global_rank, group=p.tp_group)
+                    # every TP peer runs the same optimizer code, so the decay
+                    # factor is known locally and does not travel
+                    if p._tp_wd_factor != 1.0:
+                        p._owned_data.mul_(p._tp_wd_factor)
+                    p._owned_data.add_(recv)
+                    p._tp_full_delta = None
+                    p._tp_full_grad = None
+                    p._reduced_grad = None
+        return lane.mark()
+
+    # ------------------------------------------------------------------ replicate-axis publish
+    def _replicate_publish_params(self) -> list[DedicatedParam]:
+        if self.replicate_size <= 1:
+            return []
+        return [p for p in self.bcast_params if p.in_owner_column and p._owned_data is not None]
+
+    def replicate_broadcast_sync(self) -> None:
+        self.replicate_broadcast_async()
+        self._pre_forward_wait()
+
+    def replicate_broadcast_async(self) -> None:
+        plist = self._replicate_publish_params()
+        if not plist:
+            return
+        if self._post_step_ticket is not None:
+            raise RuntimeError(
+                f"group {self.name}: a post-step publish is already in flight; "
+                "run a forward pass (or wait_all_replicate_broadcasts) before the next optimizer step"
+            )
+        ctx = self.comm_ctx
+        lane = ctx.replicate_broadcast_lane
+        lane.follow_current()
+        limit = ctx.replicate_broadcast_bucket_bytes
+        with lane.use(), torch.no_grad():
+            with ctx.time_region("post_step", self.name, "replicate_broadcast", lane):
+                by_src: dict[int, list[DedicatedParam]] = defaultdict(list)
+                for p in plist:
+                    by_src[p.owner_replicate].append(p)
+                for r, group_params in sorted(by_src.items()):
+                    src = self._global_rank(self.replicate_group, r)
+                    bucket, nbytes = [], 0
+                    for p in group_params:
+                        bucket.append(p)
+                        nbytes += p._owned_data.numel() * p._owned_data.element_size()
+                        if limit and nbytes >= limit:
+                            self._broadcast_bucket(bucket, src, lane)
+                            bucket, nbytes = [], 0
+                    if bucket:
+                        self._broadcast_bucket(bucket, src, lane)
+        self._post_step_ticket = lane.mark()
+
+    def _broadcast_bucket(self, bucket: list[DedicatedParam], src: int, lane: Lane) -> None:
+        with record_function(f"dmuon.replicate_broadcast.src{src}.params{len(bucket)}.{self.name}"):
+            for p in bucket:
+                lane.keep_alive(p._owned_data)
+                dist.broadcast(p._owned_data, src=src, group=self.replicate_group)
+
+    def post_step_publish_async(self) -> None:
+        """Whatever this placement needs after the optimizer step."""
+        t = self.tp_scatter_delta()
+        if t is not None:
+            self._tp_ticket = t
+        self.replicate_broadcast_async()
+
+    def _pre_forward_wait(self) -> None:
+        """Consume the previous step's asynchronous publish before reading masters."""
+        t = getattr(self, "_tp_ticket", None)
+        if t is not None:
+            t.wait_on_current()
+            t.wait_on(self.comm_ctx.broadcast_lane)
+            self._tp_ticket = None
+            self.comm_ctx.count(self.name, "tp_publish_waits")
+        if self._post_step_ticket is not None:
+            self._post_step_ticket.wait_on_current()
+            self._post_step_ticket.wait_on(self.comm_ctx.broadcast_lane)
+            self._post_step_ticket = None
+            self.comm_ctx.count(self.name, "replicate_publish_waits")
+
+    def has_pending_post_step(self) -> bool:
+        return self._post_step_ticket is not None or getattr(self, "_tp_ticket", None) is not None
+
+    # ------------------------------------------------------------------ ordering helpers
+    def _record_post_forward(self) -> None:
+        order = self.comm_ctx.post_forward_order
+        if self._post_forward_index is None:
+            self._post_forward_index = len(order)
+            order.append(self)
+
+    def _backward_prefetch(self) -> None:
+        """Start the publish of the group that ran forward just before this one
+        (the next one backward reaches), unless its backward already ran."""
+        if not self.reshard_after_forward or self._post_forward_index is None:
+            return
+        order = self.comm_ctx.post_forward_order
+        i = self._post_forward_index - 1
+        while i >= 0:
+            g = order[i]
+            if not g._backward_done:
+                g.unshard(prefetch=True)
+                return
+            i -= 1
+
+    def owned_params(self) -> list[DedicatedParam]:
+        return [p for p in self.params if p.is_owner]
+
+    def __repr__(self) -> str:
+        return f"{type(self).__name__}({self.name}, params={len(self.params)}, mode={self.mode})"
+
+
+class DedicatedParamGroupDDP(DedicatedParamGroup):
+    """Replicated placement: parameters stay resident, only gradients and the
+    owner's update travel."""
+
+    mode = "ddp"
+
+    def __init__(self, params, module, comm_ctx, dp_group, *, name: str = "", **_ignored):
+        super().__init__(params, module, comm_ctx, dp_group, reshard_after_forward=False, name=name)
+        self._is_unsharded = True
+
+    def post_step_broadcast_sync(self) -> None:
+        self.post_step_broadcast_async()
+        self._pre_forward_wait()
+
+    def post_step_broadcast_async(self) -> None:
+        plist = [p for p in self.bcast_params if p._owned_data is not None]
+        if not plist or self.shard_size <= 1:
+            for p in plist:
+                p.copy_owned_to_live()
+            return
+        if self._post_step_ticket is not None:
+            raise RuntimeError(
+                f"group {self.name}: a post-step broadcast is already in flight; "
+                "run a forward pass before the next optimizer step"
+            )
+        lane = self.comm_ctx.broadcast_lane
+        lane.follow_current()
+        with lane.use(), torch.no_grad():
+            with record_function(f"dmuon.ddp_post_step_broadcast.{self.name}"):
+                for p in plist:
+                    if p.tp_group is not None and not p.is_owner:
+                        pass
+                    dist.broadcast(p._owned_data, src=self._global_rank(self.dp_group, p.owner_shard), group=self.dp_group)
+                live = [p._unsharded_param for p in plist]
+                with torch.autograd._unsafe_preserve_version_counter(live):
+                    for p in plist:
+                        p.copy_owned_to_live()
+        self._post_step_ticket = lane.mark()
+
+    def post_step_publish_async(self) -> None:
+        t = self.tp_scatter_delta(lane=self.comm_ctx.broadcast_lane)
+        if t is not None:
+            t.wait_on(self.comm_ctx.broadcast_lane)
+        self.post_step_broadcast_async()

@@ -181,7 +181,7 @@ class DedicatedParamGroup:
             alloc_storage(p._flat_full)
         lane.follow_current()
         live = [p._unsharded_param for p in self.params]
-        with lane.use(), torch.no_grad(), torch.autograd._unsafe_preserve_version_counter(live):
+        with lane.use(), torch.no_grad(), torch.autograd._unsafe_preserve_version_counter(tuple(live)):
             with ctx.time_region("forward", self.name, "unshard", lane):
                 for s, plist in sorted(self._pub_by_shard.items()):
                     buf = self._packed[s]
@@ -393,7 +393,7 @@ class DedicatedParamGroup:
     def tp_gather_grads(self, lane: Optional[Lane] = None) -> None:
         """Collect the reduced shards of every TP-sharded parameter on its TP
         owner.  Every TP peer of a DP owner takes part, in parameter order."""
-        todo = [p for p in self.tp_params if p.is_owner and p._reduced_grad is not None]
+        todo = [p for p in self.tp_params if p.is_owner and p._dmuon_route == "muon" and p._reduced_grad is not None]
         if not todo:
             return
         lane = lane or self.comm_ctx.reduce_lane
@@ -427,7 +427,10 @@ class DedicatedParamGroup:
     def tp_scatter_delta(self, lane: Optional[Lane] = None) -> Optional[Ticket]:
         """Send every TP peer its slice of the owner's pre-scaled update and
         apply ``w = w * wd_factor + slice`` to the master shard."""
-        todo = [p for p in self.tp_params if p.is_owner and (p._reduced_grad is not None or p._tp_full_delta is not None)]
+        todo = [
+            p for p in self.tp_params
+            if p.is_owner and p._dmuon_route == "muon" and (p._reduced_grad is not None or p._tp_full_delta is not None)
+        ]
         if not todo:
             return None
         lane = lane or self.comm_ctx.replicate_broadcast_lane
@@ -589,7 +592,7 @@ class DedicatedParamGroupDDP(DedicatedParamGroup):
                         pass
                     dist.broadcast(p._owned_data, src=self._global_rank(self.dp_group, p.owner_shard), group=self.dp_group)
                 live = [p._unsharded_param for p in plist]
-                with torch.autograd._unsafe_preserve_version_counter(live):
+                with torch.autograd._unsafe_preserve_version_counter(tuple(live)):
                     for p in plist:
                         p.copy_owned_to_live()
         self._post_step_ticket = lane.mark()

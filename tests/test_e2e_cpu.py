@@ -1,0 +1,126 @@
+"""End-to-end correctness on CPU: 2 gloo ranks, FSDP2 + dedicated Muon on a
+4-layer decoder with tied embeddings, against a single-process Muon."""
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from dist_utils import run_ranks
+
+STEPS = 10
+HP = dict(lr=0.02, momentum=0.95, weight_decay=0.1, adamw_lr=1e-3, adamw_wd=0.01, betas=(0.9, 0.999), eps=1e-8)
+
+
+def _pred(name, p):
+    return "proj" in name and p.ndim == 2
+
+
+def _data(step: int):
+    g = torch.Generator().manual_seed(1000 + step)
+    ids = torch.randint(0, 1024, (4, 129), generator=g)
+    return ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
+
+
+def _build_model():
+    from dmuon_b200.models.llama import LlamaConfig, LlamaModel
+
+    torch.manual_seed(0)
+    return LlamaModel(LlamaConfig.tiny())
+
+
+def oracle_run(steps=STEPS):
+    """Plain single-process Muon + AdamW with the same update rules."""
+    from dmuon_b200.optim.newton_schulz import gram_newton_schulz
+
+    model = _build_model()
+    params = dict(model.named_parameters())
+    mom = {n: torch.zeros_like(p) for n, p in params.items() if _pred(n, p)}
+    adam = {n: dict(m=torch.zeros_like(p), v=torch.zeros_like(p), t=0) for n, p in params.items() if not _pred(n, p)}
+    losses = []
+    for s in range(steps):
+        x, y = _data(s)
+        loss = model(x, labels=y)
+        model.zero_grad()
+        loss.backward()
+        losses.append(loss.item())
+        with torch.no_grad():
+            for n, p in params.items():
+                g = p.grad
+                if n in mom:
+                    buf = mom[n]
+                    buf.mul_(HP["momentum"]).add_(g)
+                    u = g.add(buf, alpha=HP["momentum"])
+                    o = gram_newton_schulz(u)
+                    p.mul_(1 - HP["lr"] * HP["weight_decay"])
+                    p.add_(o, alpha=-HP["lr"] * 0.2 * math.sqrt(max(p.shape)))
+                else:
+                    st = adam[n]
+                    st["t"] += 1
+                    b1, b2 = HP["betas"]
+                    p.mul_(1 - HP["adamw_lr"] * HP["adamw_wd"])
+                    st["m"].mul_(b1).add_(g, alpha=1 - b1)
+                    st["v"].mul_(b2).addcmul_(g, g, value=1 - b2)
+                    denom = (st["v"].sqrt() / math.sqrt(1 - b2 ** st["t"])).add_(HP["eps"])
+                    p.addcdiv_(st["m"], denom, value=-HP["adamw_lr"] / (1 - b1 ** st["t"]))
+    return losses, {n: p.detach().clone() for n, p in params.items()}
+
+
+def _dist_body(rank, world, reshard, steps):
+    import torch.distributed as dist
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+
+    mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("dp",))
+    model = _build_model()
+    owners = dmuon.dedicate_params(model, mesh, _pred, reshard_after_forward=reshard)
+    for layer in model.layers:
+        fully_shard(layer, mesh=mesh)
+    fully_shard(model, mesh=mesh)
+    opt = dmuon.Muon(
+        model, lr=HP["lr"], ns_steps=5, adamw_lr=HP["adamw_lr"], weight_decay=HP["weight_decay"],
+        momentum=HP["momentum"], adamw_weight_decay=HP["adamw_wd"],
+    )
+    losses = []
+    per = 4 // world
+    for s in range(steps):
+        x, y = _data(s)
+        x, y = x[rank * per : (rank + 1) * per], y[rank * per : (rank + 1) * per]
+        loss = model(x, labels=y)
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        lt = loss.detach().clone()
+        dist.all_reduce(lt)
+        losses.append((lt / world).item())
+    sd = dmuon.get_model_state_dict(model, rank0_only=False)
+    n_owned = len(dmuon.get_owned_params(model))
+    return losses, sd, n_owned, sorted(set(int(v) for v in owners.values()))
+
+
+@pytest.mark.parametrize("reshard", [False, True])
+def test_two_rank_fsdp2_muon_matches_single_process(reshard):
+    ref_losses, ref_params = oracle_run()
+    results = run_ranks(_dist_body, 2, args=(reshard, STEPS))
+    losses, sd, n0, owners = results[0]
+    assert owners == [0, 1]
+    assert n0 + results[1][2] == 28
+    for a, b in zip(losses, ref_losses):
+        assert abs(a - b) < 2e-4 * max(1.0, abs(b)), (losses, ref_losses)
+    assert set(sd) == set(ref_params) | {"lm_head.weight"} or set(sd) == set(ref_params)
+    for n, p in ref_params.items():
+        err = (sd[n].float() - p).abs().max().item()
+        assert err < 5e-4, (n, err)
+    # both ranks return identical full state
+    for n in sd:
+        assert torch.equal(sd[n], results[1][1][n])
+
+
+def test_single_rank_world():
+    ref_losses, _ = oracle_run(3)
+    (losses, sd, n_owned, owners), = run_ranks(_dist_body, 1, args=(True, 3))
+    assert n_owned == 28 and owners == [0]
+    for a, b in zip(losses, ref_losses):
+        assert abs(a - b) < 1e-4

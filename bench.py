@@ -1,0 +1,408 @@
+#!/usr/bin/env python
+"""Headline benchmark: full training step (forward + backward + optimizer) of a
+Llama-3-8B-shaped decoder under FSDP2 + dedicated Muon, bf16 compute with fp32
+master weights and optimizer state, synthetic tokens, random-init weights.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 5 --warmup 3
+    python bench.py --impl reference ...        # the unmodified reference from baseline/_ref
+
+Rank 0 prints one JSON line.  ``value`` is the device-timed step time in ms
+(max over ranks); ``e2e`` is the same step driven through the public API with
+the token batch copied from pinned host memory and the loss read back every
+step.  Per-GPU work is fixed (weak scaling): micro-batch x seq tokens per GPU.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+
+MODELS = {
+    # name: (d_model, layers, heads, kv_heads, head_dim, ffn, vocab, default seq, default micro-batch)
+    "llama3-8b": (4096, 32, 32, 8, 128, 14336, 128256, 8192, 1),
+    "llama3.2-3b": (3072, 28, 24, 8, 128, 8192, 128256, 4096, 2),
+    "llama-1b": (2048, 16, 32, 8, 64, 8192, 128256, 4096, 2),
+    "tiny": (256, 4, 4, 4, 64, 1024, 1024, 128, 4),
+}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--model", choices=tuple(MODELS), default="llama3-8b")
+    ap.add_argument("--seq", type=int, default=0)
+    ap.add_argument("--micro-batch", type=int, default=0)
+    ap.add_argument("--optimizer", choices=("muon", "adamw"), default="muon")
+    ap.add_argument("--parallelism", default="fsdp", help="fsdp | hsdpRxS (e.g. hsdp2x4) | ddp")
+    ap.add_argument("--reshard-after-forward", action="store_true", help="drop published weights after forward")
+    ap.add_argument("--ns", choices=("gram", "direct"), default="gram")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--act-ckpt", action="store_true", help="checkpoint every decoder layer")
+    ap.add_argument("--momentum-dtype", choices=("fp32", "bf16"), default="fp32")
+    return ap.parse_args()
+
+
+def init_dist():
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29511")
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed
+    region runs (rank 0 only)."""
+
+    FIELDS = (
+        "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+        "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    )
+
+    def __init__(self, enabled: bool):
+        self.enabled = enabled
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        if not self.enabled:
+            return
+        fd, self.path = tempfile.mkstemp(suffix=".csv")
+        os.close(fd)
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL,
+            )
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if not self.enabled or self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    clk, cmax, pw = float(f[1]), float(f[2]), float(f[3])
+                except ValueError:
+                    continue
+                if pw > 250:                      # under load
+                    sm.append(clk)
+                mx.append(cmax)
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        finally:
+            try:
+                os.unlink(self.path)
+            except OSError:
+                pass
+        return {
+            "sm_mhz": statistics.median(sm) if sm else None,
+            "sm_max_mhz": max(mx) if mx else None,
+            "reasons": sorted(reasons),
+            "samples_under_load": len(sm),
+        }
+
+
+def model_dims(args):
+    d, L, h, kv, hd, ffn, vocab, seq, mb = MODELS[args.model]
+    return dict(d_model=d, n_layers=L, n_heads=h, n_kv_heads=kv, head_dim=hd, ffn_hidden=ffn, vocab_size=vocab,
+                seq=args.seq or seq, mb=args.micro_batch or mb)
+
+
+def make_mesh(args, world):
+    from torch.distributed.device_mesh import init_device_mesh
+
+    par = args.parallelism
+    if par.startswith("hsdp"):
+        r, s = (int(x) for x in par[4:].split("x"))
+        assert r * s == world, f"{par} needs {r * s} ranks, got {world}"
+        mesh2 = init_device_mesh("cuda", (r, s), mesh_dim_names=("replicate", "shard"))
+        return mesh2, mesh2["shard"], mesh2["replicate"]
+    mesh = init_device_mesh("cuda", (world,), mesh_dim_names=("dp",))
+    return mesh, mesh, None
+
+
+def _pred(name, p):
+    return "proj" in name and p.ndim == 2
+
+
+def build_ours(args, dims, rank, world, device):
+    import torch
+    from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
+
+    sys.path.insert(0, ROOT)
+    import dmuon_b200 as dmuon
+    from dmuon_b200.models.llama import LlamaConfig, LlamaModel
+
+    cfg = LlamaConfig(
+        vocab_size=dims["vocab_size"], d_model=dims["d_model"], n_layers=dims["n_layers"], n_heads=dims["n_heads"],
+        n_kv_heads=dims["n_kv_heads"], head_dim=dims["head_dim"], ffn_hidden=dims["ffn_hidden"], rope_theta=500000.0,
+    )
+    torch.manual_seed(42)
+    with torch.device(device):
+        model = LlamaModel(cfg)
+    mesh_all, shard_mesh, rep_mesh = make_mesh(args, world)
+    mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.bfloat16)
+    fsdp_mesh = mesh_all
+    if args.act_ckpt:
+        from torch.distributed.algorithms._checkpoint.checkpoint_wrapper import checkpoint_wrapper
+
+        for i, layer in enumerate(model.layers):
+            model.layers[i] = checkpoint_wrapper(layer)
+    if args.optimizer == "muon":
+        policy = None
+        if args.momentum_dtype == "bf16":
+            policy = {"defaults": {"param_dtype": "bf16", "optim_dtype": "bf16"}}
+        if args.parallelism == "ddp":
+            model.to(torch.bfloat16)
+            dmuon.dedicate_params_ddp(model, shard_mesh, _pred, compute_dtype=torch.bfloat16, param_policy=policy)
+            dmuon.replicate(model, shard_mesh)
+        else:
+            dmuon.dedicate_params(
+                model, shard_mesh, _pred, compute_dtype=None if policy else torch.bfloat16,
+                reshard_after_forward=args.reshard_after_forward, replicate_mesh=rep_mesh, param_policy=policy,
+            )
+            for layer in model.layers:
+                fully_shard(layer, mesh=fsdp_mesh, mp_policy=mp)
+            fully_shard(model, mesh=fsdp_mesh, mp_policy=mp)
+        opt = dmuon.Muon(model, lr=0.02, ns_steps=5, adamw_lr=1e-3, weight_decay=0.1,
+                         ns_backend=dmuon.NewtonSchulz(backend=args.ns))
+    else:
+        for layer in model.layers:
+            fully_shard(layer, mesh=fsdp_mesh, mp_policy=mp)
+        fully_shard(model, mesh=fsdp_mesh, mp_policy=mp)
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-3, weight_decay=0.01, fused=True)
+
+    def fwd_bwd(ids, labels):
+        loss = model(ids, labels=labels)
+        loss.backward()
+        return loss
+
+    def launches():
+        from dmuon_b200.ops import multi_tensor as MT
+
+        return MT.launch_count()
+
+    return fwd_bwd, opt, launches
+
+
+def build_reference(args, dims, rank, world, device):
+    """The unmodified reference installed under baseline/_ref, driven through
+    its public API the way its own LLM benchmark does (Hugging Face Llama,
+    dedicate_params -> fully_shard -> Muon)."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "dmuon")):
+        raise RuntimeError("baseline/_ref/dmuon is missing (reference not installed)")
+    sys.path[:] = [p for p in sys.path if os.path.abspath(p or ".") != ROOT]
+    sys.path.insert(0, ref_dir)
+    import torch
+    from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    import dmuon  # the reference package
+
+    assert os.path.abspath(dmuon.__file__).startswith(ref_dir), dmuon.__file__
+    config = LlamaConfig(
+        hidden_size=dims["d_model"], intermediate_size=dims["ffn_hidden"], num_hidden_layers=dims["n_layers"],
+        num_attention_heads=dims["n_heads"], num_key_value_heads=dims["n_kv_heads"], head_dim=dims["head_dim"],
+        vocab_size=dims["vocab_size"], max_position_embeddings=dims["seq"], rope_theta=500000.0, use_cache=False,
+        tie_word_embeddings=False, attn_implementation="sdpa",
+    )
+    torch.manual_seed(42)
+    with torch.device(device):
+        model = LlamaForCausalLM(config)
+    if args.act_ckpt:
+        model.gradient_checkpointing_enable()
+    mesh_all, shard_mesh, rep_mesh = make_mesh(args, world)
+    mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.bfloat16)
+    if args.optimizer == "muon":
+        dmuon.dedicate_params(model, shard_mesh, _pred, compute_dtype=torch.bfloat16,
+                              reshard_after_forward=args.reshard_after_forward, replicate_mesh=rep_mesh)
+        for layer in model.model.layers:
+            fully_shard(layer, mesh=mesh_all, mp_policy=mp)
+        fully_shard(model, mesh=mesh_all, mp_policy=mp)
+        opt = dmuon.Muon(model, lr=0.02, ns_steps=5, adamw_lr=1e-3, weight_decay=0.1)
+    else:
+        for layer in model.model.layers:
+            fully_shard(layer, mesh=mesh_all, mp_policy=mp)
+        fully_shard(model, mesh=mesh_all, mp_policy=mp)
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-3, weight_decay=0.01, fused=True)
+
+    def fwd_bwd(ids, labels):
+        out = model(input_ids=ids, labels=labels)
+        out.loss.backward()
+        return out.loss
+
+    return fwd_bwd, opt, (lambda: 0)
+
+
+def run(args):
+    import torch
+    import torch.distributed as dist
+
+    rank, world, local = init_dist()
+    device = torch.device("cuda", local)
+    dims = model_dims(args)
+    build = build_ours if args.impl == "ours" else build_reference
+    fwd_bwd, opt, launches = build(args, dims, rank, world, device)
+    mb, seq, vocab = dims["mb"], dims["seq"], dims["vocab_size"]
+
+    gen = torch.Generator().manual_seed(1234 + rank)
+    n_batches = 4
+    host = [torch.randint(0, vocab, (mb, seq + 1), generator=gen).pin_memory() for _ in range(n_batches)]
+    dev_batches = [h.to(device) for h in host]
+
+    def step_device(i):
+        b = dev_batches[i % n_batches]
+        opt.zero_grad()
+        loss = fwd_bwd(b[:, :-1], b[:, 1:])
+        return loss
+
+    def step_e2e(i):
+        b = host[i % n_batches].to(device, non_blocking=True)
+        opt.zero_grad()
+        loss = fwd_bwd(b[:, :-1], b[:, 1:])
+        opt.step()
+        return float(loss.item())          # device -> host read of the step's result
+
+    def sync():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        step_device(i)
+        opt.step()
+    sync()
+
+    sampler = ClockSampler(rank == 0)
+    sampler.start()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps + 1)]
+    l0 = launches()
+    sync()
+    ev[0].record()
+    for i in range(args.steps):
+        loss = step_device(i)
+        ev[2 * i + 1].record()
+        opt.step()
+        ev[2 * i + 2].record()
+    sync()
+    total_ms = ev[0].elapsed_time(ev[2 * args.steps])
+    opt_ms = sum(ev[2 * i + 1].elapsed_time(ev[2 * i + 2]) for i in range(args.steps)) / args.steps
+    l1 = launches()
+    last_loss = float(loss.item())
+
+    e2e_ms = None
+    if not args.no_e2e:
+        sync()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(args.steps):
+            last_loss = step_e2e(i)
+        b.record()
+        sync()
+        e2e_ms = a.elapsed_time(b) / args.steps
+    clocks = sampler.stop()
+
+    t = torch.tensor([total_ms / args.steps, opt_ms, e2e_ms or 0.0], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    step_ms, opt_ms, e2e_max = (float(x) for x in t.tolist())
+    peak = torch.tensor([torch.cuda.max_memory_allocated() / 2**30], device=device)
+    dist.all_reduce(peak, op=dist.ReduceOp.MAX)
+    tokens = mb * seq * world
+    if rank == 0:
+        out = {
+            "metric": "train_step_ms",
+            "value": round(step_ms, 3),
+            "unit": "ms/step",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": max(args.warmup, 3),
+            "ms_per_step": round(step_ms, 3),
+            "higher_is_better": False,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "bf16",
+            "data": "synthetic uniform token ids, random-init weights N(0, 0.02)",
+            "impl": args.impl,
+            "tokens_per_s": round(tokens / (step_ms / 1e3), 1),
+            "optimizer_step_ms": round(opt_ms, 3),
+            "fwd_bwd_ms": round(step_ms - opt_ms, 3),
+            "loss": last_loss,
+            "peak_mem_gib": round(float(peak.item()), 2),
+            "gpu_launches": int(l1 - l0),
+            "clocks": clocks,
+            "config": {
+                "model": args.model,
+                "optimizer": args.optimizer,
+                "global_batch": mb * world,
+                "micro_batch_per_gpu": mb,
+                "seq_len": seq,
+                "parallelism": (args.parallelism if args.parallelism != "fsdp" else f"fsdp{world}")
+                + ("-z3" if args.reshard_after_forward else "-z2"),
+                "newton_schulz": args.ns,
+                "activation_checkpointing": bool(args.act_ckpt),
+                "l2": "per-step working set (weights + activations, tens of GB) is far larger than the 126 MB L2",
+            },
+        }
+        if e2e_ms is not None:
+            out["e2e"] = {
+                "value": round(e2e_max, 3),
+                "unit": "ms/step",
+                "tokens_per_s": round(tokens / (e2e_max / 1e3), 1),
+                "h2d_bytes_per_step": int(mb * (seq + 1) * 8),
+                "d2h_bytes_per_step": 4,
+            }
+        print(json.dumps(out), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        try:
+            run(args)
+        except Exception as exc:  # the reference could not run here: say why, exit 0
+            import traceback
+
+            traceback.print_exc(file=sys.stderr)
+            if int(os.environ.get("RANK", "0")) == 0:
+                why = f"{type(exc).__name__}: {str(exc).splitlines()[0] if str(exc) else ''}"[:300]
+                print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
+            sys.exit(0)
+    else:
+        run(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,247 @@
+"""sm_100a kernels against plain PyTorch fp32 references (needs a B200)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+def _ref_gemm(A, B, a_mn, b_mn, C, alpha, beta, diag):
+    Af = A.float().transpose(-1, -2) if a_mn else A.float()
+    Bf = B.float().transpose(-1, -2) if b_mn else B.float()
+    D = alpha * Af @ Bf.transpose(-1, -2)
+    if C is not None:
+        D = D + beta * C.float()
+    if diag:
+        D = D + diag * torch.eye(D.shape[-2], D.shape[-1], device=D.device)
+    return D
+
+
+CASES = [
+    # M, N, K, batch, a_mn, b_mn, bn, symmetric, dtype, out dtype, epilogue
+    (128, 128, 64, 1, False, False, 128, False, torch.bfloat16, torch.bfloat16, False),
+    (512, 768, 1024, 1, False, False, 256, False, torch.bfloat16, torch.bfloat16, False),
+    (200, 300, 136, 1, False, False, 128, False, torch.bfloat16, torch.bfloat16, True),
+    (256, 256, 512, 5, False, False, 128, False, torch.float16, torch.float16, False),
+    (256, 512, 512, 2, False, False, 256, False, torch.bfloat16, torch.float32, True),
+    (512, 512, 1024, 1, False, False, 128, True, torch.bfloat16, torch.bfloat16, True),
+    (1152, 1152, 4304, 1, False, False, 256, True, torch.bfloat16, torch.bfloat16, False),
+    (256, 512, 512, 1, False, True, 256, False, torch.bfloat16, torch.bfloat16, False),
+    (256, 512, 512, 1, True, False, 256, False, torch.bfloat16, torch.bfloat16, False),
+    (384, 512, 448, 1, True, True, 128, False, torch.bfloat16, torch.bfloat16, False),
+    (512, 512, 1024, 2, True, True, 256, True, torch.bfloat16, torch.bfloat16, True),
+]
+
+
+@pytest.mark.parametrize("case", CASES, ids=[f"case{i}" for i in range(len(CASES))])
+def test_gemm_matches_fp32(case):
+    from dmuon_b200.ops import gemm as G
+
+    M, N, K, batch, a_mn, b_mn, bn, sym, dt, odt, epi = case
+    dev = _dev()
+    torch.manual_seed(0)
+    if sym:
+        X = (torch.randn(batch, M, K, device=dev) * 0.1).to(dt)
+        A = X.transpose(1, 2).contiguous() if a_mn else X
+        B = X.transpose(1, 2).contiguous() if b_mn else X
+    else:
+        A = ((torch.randn(batch, K, M, device=dev) if a_mn else torch.randn(batch, M, K, device=dev)) * 0.1).to(dt)
+        B = ((torch.randn(batch, K, N, device=dev) if b_mn else torch.randn(batch, N, K, device=dev)) * 0.1).to(dt)
+    C = None
+    alpha, beta, diag = 1.0, 0.0, 0.0
+    if epi:
+        C = torch.randn(batch, M, N, device=dev)
+        if sym:
+            C = C + C.transpose(1, 2)
+        C = C.to(odt)
+        alpha, beta, diag = 1.5, -0.5, (0.3 if M == N else 0.0)
+    out = torch.full((batch, M, N), float("nan"), device=dev, dtype=odt)
+    out2 = torch.full((batch, M, N), float("nan"), device=dev, dtype=torch.bfloat16) if odt == torch.float32 else None
+    G.gemm(A, B, out, a_mn=a_mn, b_mn=b_mn, C=C, alpha=alpha, beta=beta, diag=diag, symmetric=sym, bn=bn, out2=out2)
+    torch.cuda.synchronize()
+    G.check_status(dev)
+    ref = _ref_gemm(A, B, a_mn, b_mn, C, alpha, beta, diag)
+    scale = ref.abs().max().item() + 1e-6
+    tol = 2e-2 if odt != torch.float32 else 2e-3
+    assert not torch.isnan(out.float()).any()
+    assert (out.float() - ref).abs().max().item() / scale < tol
+    if out2 is not None:
+        assert (out2.float() - ref).abs().max().item() / scale < 2e-2
+
+
+def test_gemm_alpha_vec_and_pointer_tables():
+    from dmuon_b200.ops import gemm as G
+
+    dev = _dev()
+    torch.manual_seed(1)
+    L, M, N, K = 3, 256, 384, 256
+    A = (torch.randn(L, M, K, device=dev) * 0.1).bfloat16()
+    B = (torch.randn(L, K, N, device=dev) * 0.1).bfloat16()
+    s = torch.tensor([0.5, 2.0, -1.0], device=dev)
+    masters = [torch.randn(M, N, device=dev) for _ in range(L)]
+    before = [m.clone() for m in masters]
+    pubs = [torch.zeros(M, N, device=dev, dtype=torch.bfloat16) for _ in range(L)]
+    tab = torch.tensor([m.data_ptr() for m in masters], dtype=torch.int64, device=dev)
+    ptab = torch.tensor([p.data_ptr() for p in pubs], dtype=torch.int64, device=dev)
+    G.gemm(A, B, None, b_mn=True, out_ptrs=tab, c_ptrs=tab, out_ld=N, out_dtype=torch.float32,
+           out2_ptrs=ptab, out2_ld=N, alpha=-0.1, beta=0.9, alpha_vec=s)
+    torch.cuda.synchronize()
+    G.check_status(dev)
+    for i in range(L):
+        ref = 0.9 * before[i] + (-0.1 * s[i]) * (A[i].float() @ B[i].float())
+        assert (masters[i] - ref).abs().max().item() < 2e-3
+        assert (pubs[i].float() - ref).abs().max().item() < 3e-2
+
+
+def test_muon_prologue_and_scales():
+    from dmuon_b200.ops import multi_tensor as MT
+
+    dev = _dev()
+    torch.manual_seed(2)
+    shapes = [(256, 512), (128, 100), (33, 7)]
+    grads = [torch.randn(s, device=dev).bfloat16() for s in shapes]
+    moms = [torch.randn(s, device=dev) for s in shapes]
+    moms0 = [m.clone() for m in moms]
+    xs = [torch.empty(s, device=dev, dtype=torch.bfloat16) for s in shapes]
+    sumsq = torch.zeros(3, device=dev)
+    gs = torch.tensor(0.5, device=dev)
+    MT.muon_prologue(grads, moms, xs, [0, 1, 2], sumsq, 0.95, True, gs)
+    scale, scale2 = torch.empty(3, device=dev), torch.empty(3, device=dev)
+    MT.norm_scales(sumsq, scale, scale2, 1e-7)
+    torch.cuda.synchronize()
+    for i in range(3):
+        g = grads[i].float() * 0.5
+        m = 0.95 * moms0[i] + g
+        u = g + 0.95 * m
+        assert torch.allclose(moms[i], m, atol=1e-5)
+        assert (xs[i].float() - u).abs().max().item() < 0.02 * u.abs().max().item()
+        assert abs(sumsq[i].item() - (u * u).sum().item()) < 1e-3 * (u * u).sum().item()
+        assert abs(scale[i].item() - 1.0 / (u.norm().item() + 1e-7)) < 1e-3 * scale[i].item()
+
+
+@pytest.mark.parametrize("pdt,gdt", [(torch.float32, torch.float32), (torch.float32, torch.bfloat16), (torch.bfloat16, torch.bfloat16)])
+def test_adamw_matches_formula(pdt, gdt):
+    from dmuon_b200.ops import multi_tensor as MT
+
+    dev = _dev()
+    torch.manual_seed(3)
+    shapes = [(1000,), (64, 129), (3,)]
+    ps = [torch.randn(s, device=dev).to(pdt) for s in shapes]
+    gs = [torch.randn(s, device=dev).to(gdt) for s in shapes]
+    ms = [torch.zeros(s, device=dev) for s in shapes]
+    vs = [torch.zeros(s, device=dev) for s in shapes]
+    ref_p = [p.float().clone() for p in ps]
+    ref_m = [m.clone() for m in ms]
+    ref_v = [v.clone() for v in vs]
+    lr, b1, b2, eps, wd = 1e-2, 0.9, 0.999, 1e-8, 0.1
+    for t in (1, 2, 3):
+        MT.adamw(ps, gs, ms, vs, [t, t + 1, t + 2], lr=lr, beta1=b1, beta2=b2, eps=eps, weight_decay=wd)
+        for i in range(3):
+            tt = t + i
+            g = gs[i].float()
+            base = ps_prev = ref_p[i]
+            if pdt != torch.float32:
+                base = base.to(pdt).float()
+            ref_m[i] = b1 * ref_m[i] + (1 - b1) * g
+            ref_v[i] = b2 * ref_v[i] + (1 - b2) * g * g
+            denom = ref_v[i].sqrt() / math.sqrt(1 - b2**tt) + eps
+            ref_p[i] = base * (1 - lr * wd) - (lr / (1 - b1**tt)) * ref_m[i] / denom
+    torch.cuda.synchronize()
+    tol = 1e-5 if pdt == torch.float32 else 3e-2
+    for i in range(3):
+        assert (ps[i].float() - ref_p[i]).abs().max().item() < tol
+        assert torch.allclose(ms[i], ref_m[i], atol=1e-5)
+
+
+def test_clip_kernels():
+    from dmuon_b200.ops import multi_tensor as MT
+
+    dev = _dev()
+    torch.manual_seed(4)
+    ts = [torch.randn(1000, device=dev), torch.randn(77, 13, device=dev).bfloat16(), torch.randn(5, device=dev).half()]
+    seg = [0, 1, 0]
+    acc = torch.zeros(2, device=dev)
+    MT.clip_sumsq(ts, seg, acc)
+    ref0 = ts[0].float().pow(2).sum() + ts[2].float().pow(2).sum()
+    ref1 = ts[1].float().pow(2).sum()
+    assert abs(acc[0].item() - ref0.item()) < 1e-3 * ref0.item()
+    assert abs(acc[1].item() - ref1.item()) < 1e-3 * ref1.item()
+    before = [t.float().clone() for t in ts]
+    MT.clip_scale(ts, seg, torch.tensor([0.5, 0.25], device=dev))
+    for t, b, c in zip(ts, before, (0.5, 0.25, 0.5)):
+        assert (t.float() - b * c).abs().max().item() < 1e-2
+
+
+def _orth_err(O):
+    m, n = O.shape
+    X = O.float() if m <= n else O.float().T
+    return (X @ X.T - torch.eye(X.shape[0], device=O.device)).abs().max().item()
+
+
+@pytest.mark.parametrize("shape", [(512, 1024), (1024, 512), (256, 2048), (1152, 4304)])
+@pytest.mark.parametrize("formulation", ["gram", "direct"])
+def test_newton_schulz_kernels_vs_fp32(shape, formulation):
+    from dmuon_b200.ops import ns_sm100
+    from dmuon_b200.optim import newton_schulz as NS
+
+    dev = _dev()
+    torch.manual_seed(5)
+    L = 3
+    Gm = torch.randn(L, *shape, device=dev)
+    coefs = list(NS.POLAR_EXPRESS_COEFFICIENTS)
+    restarts = [2] if formulation == "gram" else []
+    out = ns_sm100.newton_schulz_batched(Gm, coefs, restarts, 1e-7, formulation, torch.bfloat16)
+    torch.cuda.synchronize()
+    from dmuon_b200.ops import gemm as G
+
+    G.check_status(dev)
+    for i in range(L):
+        if formulation == "gram":
+            ref = NS.gram_newton_schulz(Gm[i], coefficients=coefs, restart_iterations=restarts, deterministic=True,
+                                        compute_dtype=torch.float32)
+        else:
+            ref = NS.direct_newton_schulz(Gm[i], coefficients=coefs, compute_dtype=torch.float32)
+        assert (out[i] - ref).abs().max().item() < 0.1
+        assert _orth_err(out[i]) < 0.35
+        cos = torch.nn.functional.cosine_similarity(out[i].flatten(), ref.flatten(), dim=0).item()
+        assert cos > 0.995
+
+
+def test_muon_update_batched_matches_reference_math():
+    from dmuon_b200.ops import ns_sm100
+    from dmuon_b200.optim import newton_schulz as NS
+
+    dev = _dev()
+    torch.manual_seed(6)
+    L, m, n = 4, 512, 1536
+    grads = [torch.randn(m, n, device=dev).bfloat16() * 1e-3 for _ in range(L)]
+    moms = [torch.randn(m, n, device=dev) * 1e-3 for _ in range(L)]
+    masters = [torch.randn(m, n, device=dev) * 0.02 for _ in range(L)]
+    pubs = [torch.zeros(m, n, device=dev, dtype=torch.bfloat16) for _ in range(L)]
+    m0 = [x.clone() for x in moms]
+    w0 = [x.clone() for x in masters]
+    coefs, restarts = list(NS.POLAR_EXPRESS_COEFFICIENTS), [2]
+    lr, wd, mu = 0.02, 0.1, 0.95
+    scale = 0.2 * math.sqrt(max(m, n))
+    ns_sm100.muon_update_batched(grads, moms, masters, mu=mu, nesterov=True, coefs=coefs, restarts=restarts,
+                                 formulation="gram", lr=lr, weight_decay=wd, update_scale=scale, publish=pubs)
+    torch.cuda.synchronize()
+    from dmuon_b200.ops import gemm as G
+
+    G.check_status(dev)
+    for i in range(L):
+        g = grads[i].float()
+        buf = mu * m0[i] + g
+        u = g + mu * buf
+        o = NS.gram_newton_schulz(u, coefficients=coefs, restart_iterations=restarts, deterministic=True,
+                                  compute_dtype=torch.float32)
+        ref = w0[i] * (1 - lr * wd) - lr * scale * o
+        assert torch.allclose(moms[i], buf, atol=1e-6)
+        upd_err = (masters[i] - ref).abs().max().item()
+        assert upd_err < 0.1 * lr * scale, upd_err
+        assert (pubs[i].float() - masters[i]).abs().max().item() < 1e-2 * masters[i].abs().max().item()

@@ -43,7 +43,8 @@ def _keep(t: torch.Tensor, cpu_offload: bool, rank0_only: bool) -> Optional[torc
     if rank0_only and _rank() != 0:
         return None
     t = t.detach()
-    return t.cpu() if cpu_offload else t.clone()
+    # .cpu() of a CPU tensor is the tensor itself: always hand out a private copy
+    return t.cpu() if (cpu_offload and t.device.type != "cpu") else t.clone()
 
 
 def _bcast(t: torch.Tensor, group, src_local: int) -> None:

@@ -1,0 +1,137 @@
+"""Placement equivalence on CPU (gloo): 1-D FSDP2, replicate x shard (HSDP),
+DDP, gradient accumulation and checkpoint round trips must all reproduce the
+same training trajectory."""
+import pytest
+import torch
+
+from dist_utils import run_ranks
+from test_e2e_cpu import HP, _build_model, _data, _pred, oracle_run
+
+
+def _setup(rank, world, mode, reshard=False):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+
+    model = _build_model()
+    if mode == "hsdp":
+        mesh = init_device_mesh("cpu", (2, world // 2), mesh_dim_names=("replicate", "shard"))
+        dmuon.dedicate_params(model, mesh["shard"], _pred, reshard_after_forward=reshard, replicate_mesh=mesh["replicate"])
+        for layer in model.layers:
+            fully_shard(layer, mesh=mesh)
+        fully_shard(model, mesh=mesh)
+    elif mode == "ddp":
+        mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("dp",))
+        dmuon.dedicate_params_ddp(model, mesh, _pred)
+        dmuon.replicate(model, mesh)
+    else:
+        mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("dp",))
+        dmuon.dedicate_params(model, mesh, _pred, reshard_after_forward=reshard)
+        for layer in model.layers:
+            fully_shard(layer, mesh=mesh)
+        fully_shard(model, mesh=mesh)
+    opt = dmuon.Muon(
+        model, lr=HP["lr"], ns_steps=5, adamw_lr=HP["adamw_lr"], weight_decay=HP["weight_decay"],
+        momentum=HP["momentum"], adamw_weight_decay=HP["adamw_wd"],
+    )
+    return dmuon, model, opt
+
+
+def _train(rank, world, model, opt, steps, start=0):
+    import torch.distributed as dist
+
+    per = 4 // world
+    losses = []
+    for s in range(start, start + steps):
+        x, y = _data(s)
+        x, y = x[rank * per : (rank + 1) * per], y[rank * per : (rank + 1) * per]
+        opt.zero_grad()
+        loss = model(x, labels=y)
+        loss.backward()
+        opt.step()
+        lt = loss.detach().clone()
+        dist.all_reduce(lt)
+        losses.append((lt / world).item())
+    return losses
+
+
+def _body_mode(rank, world, mode, reshard, steps):
+    dmuon, model, opt = _setup(rank, world, mode, reshard)
+    losses = _train(rank, world, model, opt, steps)
+    sd = dmuon.get_model_state_dict(model, rank0_only=False)
+    plan = dmuon.summarize_comm_plan(model)
+    groups = dmuon.summarize_param_groups(opt)
+    return losses, sd, plan["owner_imbalance"], len(groups)
+
+
+@pytest.mark.parametrize("mode,reshard", [("fsdp", False), ("hsdp", False), ("hsdp", True), ("ddp", False)])
+def test_four_rank_placements_match_single_process(mode, reshard):
+    steps = 5
+    ref_losses, ref_params = oracle_run(steps)
+    res = run_ranks(_body_mode, 4, args=(mode, reshard, steps))
+    losses, sd, imb, ngroups = res[0]
+    assert ngroups == 2
+    for a, b in zip(losses, ref_losses):
+        assert abs(a - b) < 2e-4 * max(1.0, abs(b)), (mode, losses, ref_losses)
+    for n, p in ref_params.items():
+        assert (sd[n].float() - p).abs().max().item() < 5e-4, n
+    for r in range(1, 4):
+        for n in sd:
+            assert torch.equal(sd[n], res[r][1][n]), (mode, r, n)
+
+
+def _body_accum(rank, world, use_no_sync):
+    import torch.distributed as dist
+
+    dmuon, model, opt = _setup(rank, world, "fsdp")
+    per = 4 // world
+    for s in range(2):
+        opt.zero_grad()
+        for micro in range(2):
+            x, y = _data(2 * s + micro)
+            x, y = x[rank * per : (rank + 1) * per], y[rank * per : (rank + 1) * per]
+            if use_no_sync and micro == 0:
+                with dmuon.no_sync(model):
+                    (model(x, labels=y) / 2).backward()
+            else:
+                (model(x, labels=y) / 2).backward()
+        opt.step()
+    return dmuon.get_model_state_dict(model, rank0_only=False)
+
+
+def test_grad_accumulation_with_and_without_no_sync():
+    a = run_ranks(_body_accum, 2, args=(False,))[0]
+    b = run_ranks(_body_accum, 2, args=(True,))[0]
+    for n in a:
+        assert (a[n].float() - b[n].float()).abs().max().item() < 1e-4, n
+
+
+def _body_ckpt(rank, world, mode):
+    dmuon, model, opt = _setup(rank, world, mode)
+    _train(rank, world, model, opt, 2)
+    msd = dmuon.get_model_state_dict(model, rank0_only=False)
+    osd = dmuon.get_optimizer_state_dict(model, opt, rank0_only=False)
+    cont = _train(rank, world, model, opt, 2, start=2)
+    # fresh model + optimizer restored from the state dicts must continue identically
+    dmuon2, model2, opt2 = _setup(rank, world, mode)
+    dmuon2.set_model_state_dict(model2, msd)
+    dmuon2.set_optimizer_state_dict(model2, opt2, osd)
+    cont2 = _train(rank, world, model2, opt2, 2, start=2)
+    keys = (sorted(osd), sorted(osd["dedicated"])[:2], len(osd["fsdp"]), len(osd["dedicated"]))
+    mom = next(iter(osd["dedicated"].values()))["momentum_buffer"]
+    return cont, cont2, keys, tuple(mom.shape), str(mom.dtype), sorted(msd)
+
+
+@pytest.mark.parametrize("mode", ["fsdp", "hsdp", "ddp"])
+def test_checkpoint_roundtrip_resumes_identically(mode):
+    world = 4 if mode == "hsdp" else 2
+    res = run_ranks(_body_ckpt, world, args=(mode,))
+    cont, cont2, keys, mshape, mdtype, names = res[0]
+    assert keys[0] == ["dedicated", "dedicated_adamw", "fsdp", "param_groups"]
+    assert keys[3] == 28 and keys[2] == 10      # 28 matrices; embedding + 9 norms
+    assert len(mshape) == 2 and mdtype == "torch.float32"
+    ref = _build_model()
+    assert names == sorted(dict(ref.named_parameters(remove_duplicate=False)))
+    for a, b in zip(cont, cont2):
+        assert abs(a - b) < 1e-5, (cont, cont2)

@@ -1,0 +1,93 @@
+#!/usr/bin/env python
+"""Run one configuration of the tcgen05 GEMM a few times (for timing or for an
+``ncu`` capture of a small case).
+
+    python benchmarks/gemm_case.py --m 4096 --n 4096 --k 4096 --batch 2 --b-mn
+    python benchmarks/gemm_case.py --m 4096 --k 14336 --batch 2 --symmetric
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--m", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=0)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--batch", type=int, default=2)
+    ap.add_argument("--bn", type=int, default=256)
+    ap.add_argument("--a-mn", action="store_true")
+    ap.add_argument("--b-mn", action="store_true")
+    ap.add_argument("--symmetric", action="store_true")
+    ap.add_argument("--fp16", action="store_true")
+    ap.add_argument("--with-c", action="store_true")
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--cublas", action="store_true", help="also time torch.bmm on the same operands")
+    args = ap.parse_args()
+    import torch
+
+    from dmuon_b200.ops import gemm as G
+
+    dev = torch.device("cuda", 0)
+    dt = torch.float16 if args.fp16 else torch.bfloat16
+    M, K, L = args.m, args.k, args.batch
+    N = M if (args.symmetric or not args.n) else args.n
+    torch.manual_seed(0)
+    A = (torch.randn(L, K, M, device=dev) if args.a_mn else torch.randn(L, M, K, device=dev)).mul_(0.05).to(dt)
+    if args.symmetric:
+        B, b_mn = A, args.a_mn
+    else:
+        b_mn = args.b_mn
+        B = (torch.randn(L, K, N, device=dev) if b_mn else torch.randn(L, N, K, device=dev)).mul_(0.05).to(dt)
+    C = torch.randn(L, M, N, device=dev).to(dt) if args.with_c else None
+    out = torch.empty(L, M, N, device=dev, dtype=dt)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def run():
+        G.gemm(A, B, out, a_mn=args.a_mn, b_mn=b_mn, C=C, beta=0.5 if C is not None else 0.0,
+               symmetric=args.symmetric, bn=args.bn)
+
+    for _ in range(args.warmup):
+        run()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(args.iters):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        run()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    G.check_status(dev)
+    ms = sorted(times)[len(times) // 2]
+    rec = {"M": M, "N": N, "K": K, "batch": L, "bn": args.bn, "a_mn": args.a_mn, "b_mn": b_mn,
+           "symmetric": args.symmetric, "ms": round(ms, 4), "dense_tflops": round(2.0 * M * N * K * L / ms / 1e9, 1)}
+    if args.cublas:
+        Af = A.transpose(1, 2) if args.a_mn else A
+        Bf = B if b_mn else B.transpose(1, 2)
+        for _ in range(args.warmup):
+            torch.bmm(Af, Bf)
+        ts = []
+        for _ in range(args.iters):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            torch.bmm(Af, Bf)
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        rec["cublas_ms"] = round(sorted(ts)[len(ts) // 2], 4)
+        rec["cublas_tflops"] = round(2.0 * M * N * K * L / rec["cublas_ms"] / 1e9, 1)
+    print(json.dumps(rec))
+
+
+if __name__ == "__main__":
+    main()

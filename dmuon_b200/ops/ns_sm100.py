@@ -125,22 +125,50 @@ def _apply(Q: torch.Tensor, X: torch.Tensor, left: bool, **kw) -> None:
         G.gemm(X, Q, kw.pop("out", None), **kw)
 
 
-def _iterate(ws: _Workspace, coefs, restarts, formulation: str, left: bool, x_is_raw: bool):
-    """Run all products but the final application.  Returns ``(Q, X, pending)``
-    where the result is ``Q X`` (times ``ws.scale`` when ``pending``)."""
+class _XScale:
+    """How the stored operand relates to the normalised matrix:
+    ``X_true = X_stored * vec[b] * h`` with an optional per-matrix device vector
+    (``vec``; ``vec2`` holds its squares) and a host factor ``h``.
+
+    bf16 operands are stored unnormalised (``vec = 1/||u||``, written by the
+    norm kernel, ``h = 1``) because bf16 has the range for raw gradients.  fp16
+    operands are stored normalised and multiplied by a power of two ``K`` near
+    ``sqrt(min(m, n))`` (``h = 1/K``) so their entries sit around
+    ``1/sqrt(max(m, n))`` instead of ``1/sqrt(m n)``, which would graze the fp16
+    subnormal range."""
+
+    def __init__(self, vec=None, vec2=None, h: float = 1.0):
+        self.vec, self.vec2, self.h = vec, vec2, float(h)
+
+
+def fp16_prescale(m0: int, n0: int) -> float:
+    import math
+
+    return float(2 ** round(math.log2(math.sqrt(min(m0, n0)))))
+
+
+def _iterate(ws: _Workspace, coefs, restarts, formulation: str, left: bool, xs: _XScale):
+    """Run all products but the final application.  Returns ``(Q, X)``: the
+    result is ``Q X_true`` (gram) or ``X`` itself (direct, which needs
+    ``X_stored == X_true``)."""
     X = ws.X
     if formulation == "direct":
-        # X <- a X + (b A + c A A) X, A = X X^T ; X was normalised by the caller
+        # X <- a X + (b A + c A A) X, A = X X^T
         Xn = ws.X2
         for a, b, c in coefs:
             _gram(ws, X, ws.R, left)
             G.gemm(ws.R, ws.R, ws.P, C=ws.R, alpha=c, beta=b, symmetric=True)
             _apply(ws.P, X, left, out=Xn, C=X, beta=a)
             X, Xn = Xn, X
-        return None, X, False
+        return None, X
 
-    pending = x_is_raw
-    _gram(ws, X, ws.R, left, alpha_vec=ws.scale2 if pending else None)
+    def gram_of(Xs, out):
+        if left:
+            G.gemm(Xs, Xs, out, symmetric=True, alpha=xs.h * xs.h, alpha_vec=xs.vec2)
+        else:
+            G.gemm(Xs, Xs, out, a_mn=True, b_mn=True, symmetric=True, alpha=xs.h * xs.h, alpha_vec=xs.vec2)
+
+    gram_of(X, ws.R)
     R, Rn = ws.R, ws.R2
     pool = (ws.Qa, ws.Qb, ws.P)
 
@@ -151,11 +179,11 @@ def _iterate(ws: _Workspace, coefs, restarts, formulation: str, left: bool, x_is
     last = len(coefs) - 1
     for i, (a, b, c) in enumerate(coefs):
         if i in restarts and i != 0:
+            # the new operand keeps the scale of the old one: Q X_stored
             Xn = ws.X2 if X is ws.X else ws.X
-            _apply(Q, X, left, out=Xn, alpha_vec=ws.scale if pending else None)
-            pending = False
+            _apply(Q, X, left, out=Xn)
             X = Xn
-            _gram(ws, X, R, left)
+            gram_of(X, R)
             Q = None
         # step polynomial P = c R R + b R + a I
         P = free(Q)
@@ -170,26 +198,24 @@ def _iterate(ws: _Workspace, coefs, restarts, formulation: str, left: bool, x_is
             G.gemm(R, P, ws.RP, symmetric=True)
             G.gemm(ws.RP, P, Rn, symmetric=True)
             R, Rn = Rn, R
-    return Q, X, pending
+    return Q, X
 
 
-def _run(
-    ws: _Workspace,
-    coefs,
-    restarts,
-    formulation: str,
-    left: bool,
-    x_is_raw: bool,
-    final_kw: dict,
-) -> None:
-    Q, X, pending = _iterate(ws, coefs, restarts, formulation, left, x_is_raw)
+def _run(ws: _Workspace, coefs, restarts, formulation: str, left: bool, xs: _XScale, final_kw: dict) -> None:
+    Q, X = _iterate(ws, coefs, restarts, formulation, left, xs)
     if formulation == "direct":
-        # the iterate itself is the result: X is already orthogonalised
-        final_kw["copy_from"] = X
+        final_kw["copy_from"] = X       # the iterate itself is the result
         return
-    if pending:
-        final_kw["alpha_vec"] = ws.scale
+    final_kw["alpha"] = float(final_kw.get("alpha", 1.0)) * xs.h
+    if xs.vec is not None:
+        final_kw["alpha_vec"] = xs.vec
     _apply(Q, X, left, **final_kw)
+
+
+def _resolve_dtype(compute_dtype, formulation: str) -> torch.dtype:
+    if compute_dtype in (torch.bfloat16, torch.float16):
+        return compute_dtype
+    return torch.float16 if formulation == "gram" else torch.bfloat16
 
 
 def newton_schulz_batched(
@@ -202,31 +228,42 @@ def newton_schulz_batched(
     out: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """Orthogonalise every matrix of ``X_in`` ``[L, m0, n0]``; returns a tensor
-    of the input dtype."""
+    of the input dtype.  ``compute_dtype`` is the operand dtype of the products
+    (default: fp16 for the Gram form, bf16 for the direct form)."""
     assert X_in.dim() == 3 and X_in.is_cuda
     L, m0, n0 = X_in.shape
-    cd = compute_dtype or torch.bfloat16
-    if cd == torch.float32:
-        cd = torch.bfloat16
+    cd = _resolve_dtype(compute_dtype, formulation)
     ws = workspace(L, m0, n0, cd, X_in.device)
     left = m0 <= n0
-    Xf = X_in.float() if X_in.dtype != torch.float32 else X_in
-    sumsq = (Xf * Xf).sum(dim=(1, 2))
-    ws.scale.copy_(1.0 / (sumsq.sqrt() + eps))
-    ws.X.copy_(Xf * ws.scale.view(-1, 1, 1))
+    K = fp16_prescale(m0, n0) if (cd == torch.float16 and formulation == "gram") else 1.0
+    if X_in.is_contiguous() and X_in.dtype in MT._DT:
+        # one read for the norms, one read + one write for the normalised operand
+        mats = [X_in[i] for i in range(L)]
+        slots = list(range(L))
+        ws.sumsq.zero_()
+        MT.clip_sumsq(mats, slots, ws.sumsq)
+        MT.norm_scales(ws.sumsq, ws.scale, ws.scale2, eps)
+        if K != 1.0:
+            ws.scale.mul_(K)
+        MT.cast(mats, [ws.X[i] for i in range(L)], scale=ws.scale, slots=slots)
+    else:
+        Xf = X_in.float()
+        sumsq = (Xf * Xf).sum(dim=(1, 2))
+        ws.scale.copy_(K / (sumsq.sqrt() + eps))
+        ws.X.copy_(Xf * ws.scale.view(-1, 1, 1))
+    xs = _XScale(h=1.0 / K)
     if out is None:
         out = torch.empty(L, m0, n0, device=X_in.device, dtype=X_in.dtype)
-    odt = out.dtype
     kw: dict = {}
     if formulation == "direct":
-        _run(ws, coefs, restarts, formulation, left, False, kw)
+        _run(ws, coefs, restarts, formulation, left, xs, kw)
         out.copy_(kw["copy_from"])
         return out
-    if odt in (torch.bfloat16, torch.float16, torch.float32):
-        kw["out"] = out
-        _run(ws, coefs, restarts, formulation, left, False, kw)
-        return out
-    raise TypeError(f"unsupported output dtype {odt}")
+    if out.dtype not in (torch.bfloat16, torch.float16, torch.float32):
+        raise TypeError(f"unsupported output dtype {out.dtype}")
+    kw["out"] = out
+    _run(ws, coefs, restarts, formulation, left, xs, kw)
+    return out
 
 
 def newton_schulz_single(G_in, coefs, restarts, eps, formulation, compute_dtype) -> torch.Tensor:
@@ -272,29 +309,33 @@ def muon_update_batched(
     m0 = g0.shape[0]
     n0 = g0.numel() // m0
     dev = g0.device
-    cd = compute_dtype or torch.bfloat16
-    if cd == torch.float32:
-        cd = torch.bfloat16
+    cd = _resolve_dtype(compute_dtype, formulation)
     ws = workspace(L, m0, n0, cd, dev)
     left = m0 <= n0
     ws.sumsq.zero_()
-    raw_ok = cd == torch.bfloat16 and formulation == "gram"
-    if raw_ok:
-        xs = [ws.X[i] for i in range(L)]
-        MT.muon_prologue(grads, moms, xs, list(range(L)), ws.sumsq, mu, nesterov, gscale)
+    slots = list(range(L))
+    if cd == torch.bfloat16 and formulation == "gram":
+        # one pass: the raw bf16 operand carries its scale as a per-matrix vector
+        MT.muon_prologue(grads, moms, [ws.X[i] for i in range(L)], slots, ws.sumsq, mu, nesterov, gscale)
         MT.norm_scales(ws.sumsq, ws.scale, ws.scale2, eps)
+        xscale = _XScale(vec=ws.scale, vec2=ws.scale2)
     else:
+        # two passes: fp32 staging, then normalise (and prescale fp16) while casting
         if ws.Xf32 is None:
             ws.Xf32 = torch.empty(L, m0, n0, device=dev, dtype=torch.float32)
-        xs = [ws.Xf32[i] for i in range(L)]
-        MT.muon_prologue(grads, moms, xs, list(range(L)), ws.sumsq, mu, nesterov, gscale)
+        stage = [ws.Xf32[i] for i in range(L)]
+        MT.muon_prologue(grads, moms, stage, slots, ws.sumsq, mu, nesterov, gscale)
         MT.norm_scales(ws.sumsq, ws.scale, ws.scale2, eps)
-        MT.cast(xs, [ws.X[i] for i in range(L)], scale=ws.scale, slots=list(range(L)))
+        K = fp16_prescale(m0, n0) if (cd == torch.float16 and formulation == "gram") else 1.0
+        if K != 1.0:
+            ws.scale.mul_(K)
+        MT.cast(stage, [ws.X[i] for i in range(L)], scale=ws.scale, slots=slots)
+        xscale = _XScale(h=1.0 / K)
 
     step_alpha = -float(lr) * float(update_scale)
     if formulation == "direct":
         kw: dict = {}
-        _run(ws, coefs, restarts, formulation, left, False, kw)
+        _run(ws, coefs, restarts, formulation, left, xscale, kw)
         O = kw["copy_from"]
         with torch.no_grad():
             for i in range(L):
@@ -324,4 +365,4 @@ def muon_update_batched(
         if publish is not None and all(p is not None for p in publish):
             kw["out2_ptrs"] = _ptr_table(publish)
             kw["out2_ld"] = n0
-    _run(ws, coefs, restarts, formulation, left, raw_ok, kw)
+    _run(ws, coefs, restarts, formulation, left, xscale, kw)

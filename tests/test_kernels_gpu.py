@@ -184,8 +184,8 @@ def _orth_err(O):
 
 
 @pytest.mark.parametrize("shape", [(512, 1024), (1024, 512), (256, 2048), (1152, 4304)])
-@pytest.mark.parametrize("formulation", ["gram", "direct"])
-def test_newton_schulz_kernels_vs_fp32(shape, formulation):
+@pytest.mark.parametrize("formulation,cdt", [("gram", torch.float16), ("gram", torch.bfloat16), ("direct", torch.bfloat16)])
+def test_newton_schulz_kernels_vs_fp32(shape, formulation, cdt):
     from dmuon_b200.ops import ns_sm100
     from dmuon_b200.optim import newton_schulz as NS
 
@@ -195,7 +195,7 @@ def test_newton_schulz_kernels_vs_fp32(shape, formulation):
     Gm = torch.randn(L, *shape, device=dev)
     coefs = list(NS.POLAR_EXPRESS_COEFFICIENTS)
     restarts = [2] if formulation == "gram" else []
-    out = ns_sm100.newton_schulz_batched(Gm, coefs, restarts, 1e-7, formulation, torch.bfloat16)
+    out = ns_sm100.newton_schulz_batched(Gm, coefs, restarts, 1e-7, formulation, cdt)
     torch.cuda.synchronize()
     from dmuon_b200.ops import gemm as G
 
@@ -206,13 +206,17 @@ def test_newton_schulz_kernels_vs_fp32(shape, formulation):
                                         compute_dtype=torch.float32)
         else:
             ref = NS.direct_newton_schulz(Gm[i], coefficients=coefs, compute_dtype=torch.float32)
-        assert (out[i] - ref).abs().max().item() < 0.1
+        assert (out[i] - ref).abs().max().item() < (0.03 if cdt == torch.float16 else 0.1)
         assert _orth_err(out[i]) < 0.35
+        if cdt == torch.float16:
+            # fp16 operands track the fp32 iteration closely
+            assert _orth_err(out[i]) < _orth_err(ref) + 0.03
         cos = torch.nn.functional.cosine_similarity(out[i].flatten(), ref.flatten(), dim=0).item()
         assert cos > 0.995
 
 
-def test_muon_update_batched_matches_reference_math():
+@pytest.mark.parametrize("cdt", [torch.float16, torch.bfloat16])
+def test_muon_update_batched_matches_reference_math(cdt):
     from dmuon_b200.ops import ns_sm100
     from dmuon_b200.optim import newton_schulz as NS
 
@@ -229,7 +233,8 @@ def test_muon_update_batched_matches_reference_math():
     lr, wd, mu = 0.02, 0.1, 0.95
     scale = 0.2 * math.sqrt(max(m, n))
     ns_sm100.muon_update_batched(grads, moms, masters, mu=mu, nesterov=True, coefs=coefs, restarts=restarts,
-                                 formulation="gram", lr=lr, weight_decay=wd, update_scale=scale, publish=pubs)
+                                 formulation="gram", lr=lr, weight_decay=wd, update_scale=scale, publish=pubs,
+                                 compute_dtype=cdt)
     torch.cuda.synchronize()
     from dmuon_b200.ops import gemm as G
 

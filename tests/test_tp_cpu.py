@@ -1,0 +1,135 @@
+"""Tensor-parallel matrices under dedicated Muon on CPU (gloo, DP2 x TP2):
+gather reduced shards to the TP owner, orthogonalise the full matrix, scatter
+the update -- must equal single-process Muon on the unsharded model."""
+import math
+
+import pytest
+import torch
+import torch.nn as nn
+
+from dist_utils import run_ranks
+
+LR, MU, WD, ALR = 0.02, 0.95, 0.1, 1e-3
+
+
+class Block(nn.Module):
+    def __init__(self, d, h):
+        super().__init__()
+        self.norm = nn.LayerNorm(d)
+        self.up_proj = nn.Linear(d, h, bias=False)
+        self.down_proj = nn.Linear(h, d, bias=False)
+
+    def forward(self, x):
+        return x + self.down_proj(torch.nn.functional.gelu(self.up_proj(self.norm(x))))
+
+
+class Net(nn.Module):
+    def __init__(self, d=32, h=64, n=3):
+        super().__init__()
+        self.inp = nn.Linear(8, d)
+        self.layers = nn.ModuleList(Block(d, h) for _ in range(n))
+        self.head = nn.Linear(d, 4)
+
+    def forward(self, x):
+        x = self.inp(x)
+        for l in self.layers:
+            x = l(x)
+        return self.head(x)
+
+
+def _pred(n, p):
+    return "proj" in n and p.ndim == 2
+
+
+def _data(step):
+    g = torch.Generator().manual_seed(77 + step)
+    return torch.randn(8, 8, generator=g), torch.randn(8, 4, generator=g)
+
+
+def _oracle(steps):
+    from dmuon_b200.optim.newton_schulz import gram_newton_schulz
+
+    torch.manual_seed(0)
+    model = Net()
+    params = dict(model.named_parameters())
+    mom = {n: torch.zeros_like(p) for n, p in params.items() if _pred(n, p)}
+    adam = {n: [torch.zeros_like(p), torch.zeros_like(p), 0] for n, p in params.items() if not _pred(n, p)}
+    losses = []
+    for s in range(steps):
+        x, y = _data(s)
+        loss = (model(x) - y).pow(2).mean()
+        model.zero_grad()
+        loss.backward()
+        losses.append(loss.item())
+        with torch.no_grad():
+            for n, p in params.items():
+                g = p.grad
+                if n in mom:
+                    mom[n].mul_(MU).add_(g)
+                    o = gram_newton_schulz(g.add(mom[n], alpha=MU))
+                    p.mul_(1 - LR * WD).add_(o, alpha=-LR * 0.2 * math.sqrt(max(p.shape)))
+                else:
+                    st = adam[n]
+                    st[2] += 1
+                    p.mul_(1 - ALR * 0.01)
+                    st[0].mul_(0.9).add_(g, alpha=0.1)
+                    st[1].mul_(0.999).addcmul_(g, g, value=0.001)
+                    den = (st[1].sqrt() / math.sqrt(1 - 0.999 ** st[2])).add_(1e-8)
+                    p.addcdiv_(st[0], den, value=-ALR / (1 - 0.9 ** st[2]))
+    return losses, {n: p.detach().clone() for n, p in params.items()}
+
+
+def _body(rank, world, mode, steps):
+    import torch.distributed as dist
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+    from torch.distributed.tensor.parallel import ColwiseParallel, RowwiseParallel, parallelize_module
+
+    import dmuon_b200 as dmuon
+
+    mesh = init_device_mesh("cpu", (2, 2), mesh_dim_names=("dp", "tp"))
+    torch.manual_seed(0)
+    model = Net()
+    for blk in model.layers:
+        parallelize_module(blk, mesh["tp"], {"up_proj": ColwiseParallel(), "down_proj": RowwiseParallel()})
+    if mode == "fsdp":
+        owners = dmuon.dedicate_params(model, mesh["dp"], _pred, reshard_after_forward=False)
+        for blk in model.layers:
+            fully_shard(blk, mesh=mesh["dp"])
+        fully_shard(model, mesh=mesh["dp"])
+    else:
+        owners = dmuon.dedicate_params_ddp_tp(model, mesh["dp"], _pred)
+        dmuon.replicate_tp(model, mesh["dp"])
+    opt = dmuon.Muon(model, lr=LR, momentum=MU, weight_decay=WD, adamw_lr=ALR)
+    dp_rank = mesh["dp"].get_local_rank()
+    losses = []
+    for s in range(steps):
+        x, y = _data(s)
+        x, y = x[dp_rank * 4 : dp_rank * 4 + 4], y[dp_rank * 4 : dp_rank * 4 + 4]
+        opt.zero_grad()
+        loss = (model(x) - y).pow(2).mean()
+        loss.backward()
+        opt.step()
+        lt = loss.detach().clone()
+        dist.all_reduce(lt, group=mesh["dp"].get_group())
+        losses.append((lt / 2).item())
+    sd = dmuon.get_model_state_dict(model, rank0_only=False)
+    tp_owned = sum(1 for p in dmuon.get_dedicated_params(model) if p.is_owner and p.is_tp_owner)
+    osd = dmuon.get_optimizer_state_dict(model, opt, rank0_only=False)
+    mshape = tuple(osd["dedicated"]["layers.0.up_proj.weight"]["momentum_buffer"].shape)
+    return losses, sd, tp_owned, mshape
+
+
+@pytest.mark.parametrize("mode", ["fsdp", "ddp_tp"])
+def test_tp_muon_matches_single_process(mode):
+    steps = 4
+    ref_losses, ref_params = _oracle(steps)
+    res = run_ranks(_body, 4, args=(mode, steps))
+    losses, sd, _, mshape = res[0]
+    assert mshape == (64, 32)
+    for a, b in zip(losses, ref_losses):
+        assert abs(a - b) < 1e-4 * max(1.0, abs(b)), (losses, ref_losses)
+    for n, p in ref_params.items():
+        assert (sd[n].float() - p).abs().max().item() < 2e-4, n
+    # six TP matrices, every one orthogonalised on exactly one rank
+    assert sum(r[2] for r in res) == 6

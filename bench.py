@@ -51,6 +51,10 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--act-ckpt", action="store_true", help="checkpoint every decoder layer")
     ap.add_argument("--momentum-dtype", choices=("fp32", "bf16"), default="fp32")
+    ap.add_argument("--comm", choices=("auto", "peer", "nccl"), default="auto",
+                    help="data plane for dedicated parameters (this package only)")
+    ap.add_argument("--attention", choices=("cudnn", "flash"), default="cudnn",
+                    help="SDPA backend preference of this package's model (the reference arm uses Hugging Face's default)")
     return ap.parse_args()
 
 
@@ -162,8 +166,10 @@ def build_ours(args, dims, rank, world, device):
 
     sys.path.insert(0, ROOT)
     import dmuon_b200 as dmuon
+    from dmuon_b200.models import llama as llama_mod
     from dmuon_b200.models.llama import LlamaConfig, LlamaModel
 
+    llama_mod.ATTENTION_BACKEND = args.attention
     cfg = LlamaConfig(
         vocab_size=dims["vocab_size"], d_model=dims["d_model"], n_layers=dims["n_layers"], n_heads=dims["n_heads"],
         n_kv_heads=dims["n_kv_heads"], head_dim=dims["head_dim"], ffn_hidden=dims["ffn_hidden"], rope_theta=500000.0,
@@ -191,6 +197,7 @@ def build_ours(args, dims, rank, world, device):
             dmuon.dedicate_params(
                 model, shard_mesh, _pred, compute_dtype=None if policy else torch.bfloat16,
                 reshard_after_forward=args.reshard_after_forward, replicate_mesh=rep_mesh, param_policy=policy,
+                comm_backend=args.comm,
             )
             for layer in model.layers:
                 fully_shard(layer, mesh=fsdp_mesh, mp_policy=mp)
@@ -213,6 +220,8 @@ def build_ours(args, dims, rank, world, device):
 
         return MT.launch_count()
 
+    ctx = getattr(model, "_dedicated_comm_ctx", None)
+    args.comm_used = "peer-memory kernels" if getattr(ctx, "peer_runtime", None) is not None else "nccl"
     return fwd_bwd, opt, launches
 
 
@@ -370,6 +379,8 @@ def run(args):
                 "parallelism": (args.parallelism if args.parallelism != "fsdp" else f"fsdp{world}")
                 + ("-z3" if args.reshard_after_forward else "-z2"),
                 "newton_schulz": args.ns,
+                "dedicated_data_plane": getattr(args, "comm_used", "nccl"),
+                "attention": (args.attention + " SDPA backend" if args.impl == "ours" else "Hugging Face sdpa default"),
                 "activation_checkpointing": bool(args.act_ckpt),
                 "l2": "per-step working set (weights + activations, tens of GB) is far larger than the 126 MB L2",
             },

@@ -225,6 +225,7 @@ def _setup(
     param_policy_fn=None,
     process_group_policy=None,
     allow_tp=True,
+    comm_backend=None,
 ):
     owner_strategy = _pick(owner_strategy, "DMUON_OWNER_STRATEGY", "lpt", ("lpt", "round_robin", "rank0"), "owner_strategy")
     owner_cost_model = _pick(owner_cost_model, "DMUON_OWNER_COST_MODEL", "optimizer", ("optimizer", "numel"), "owner_cost_model")
@@ -348,6 +349,23 @@ def _setup(
 
     states: list[DedicatedState] = []
     group_cls = DedicatedParamGroup if mode == "fsdp" else DedicatedParamGroupDDP
+    # data plane: peer-memory kernels where the placement allows it, else collectives
+    from .parallel import peer as peer_mod
+
+    want = (comm_backend or peer_mod.peer_backend_requested()).lower()
+    if want not in ("auto", "peer", "nccl", "collective"):
+        raise ValueError(f"comm_backend must be 'auto', 'peer' or 'nccl', got {want!r}")
+    use_peer = False
+    if mode == "fsdp" and want in ("auto", "peer"):
+        why_not = peer_mod.peer_backend_possible(device, dp_group, rep_group, [d for v in grouped.values() for d in v])
+        if why_not is None:
+            use_peer = True
+        elif want == "peer":
+            raise RuntimeError(f"comm_backend='peer' is not possible here: {why_not}")
+        else:
+            log.info("dedicate_params: collective data plane (%s)", why_not)
+    if use_peer:
+        group_cls = peer_mod.PeerParamGroup
     for (hook_mod, _key), dparams in grouped.items():
         gname = index.module_fqn.get(id(hook_mod), "") or type(hook_mod).__name__
         group = group_cls(
@@ -361,6 +379,9 @@ def _setup(
         )
         states.append(DedicatedState(hook_mod, group, ctx))
     _link_forward_order(index, states, ctx)
+    ctx.peer_runtime = None
+    if use_peer:
+        ctx.peer_runtime = peer_mod.PeerRuntime(ctx, dp_group, [st.group for st in ctx.all_states])
     model._dedicated_comm_ctx = ctx
     ctx.tp_groups = list(tp_groups.values())
     return dict(assignment.dp_owners)
@@ -391,6 +412,7 @@ def dedicate_params(
     param_policy=None,
     param_policy_fn=None,
     process_group_policy: Optional[str] = None,
+    comm_backend: Optional[str] = None,
 ) -> dict:
     """Dedicated ownership on top of FSDP2 (call before ``fully_shard``).
 
@@ -401,8 +423,13 @@ def dedicate_params(
     coordinate: gradients are averaged over the shard axis, then the replicate
     axis, and the owner's update is copied to the other replicate rows after
     the step.
+
+    ``comm_backend`` (not in the reference): ``"peer"`` moves dedicated data with
+    peer-memory kernels over NVLink (one shard axis of at most 8 GPUs, no tensor
+    parallelism), ``"nccl"`` uses collectives, ``"auto"`` (default, also
+    ``DMUON_COMM_BACKEND``) picks peer memory where it is possible.
     """
-    if mesh.ndim != 1 or (replicate_mesh is not None and replicate_mesh.ndim != 1):
+    if getattr(mesh, "ndim", 1) != 1 or (replicate_mesh is not None and getattr(replicate_mesh, "ndim", 1) != 1):
         raise ValueError("dedicate_params expects 1-D meshes for the shard and the replicate axis")
     return _setup(
         model,
@@ -429,6 +456,7 @@ def dedicate_params(
         param_policy=param_policy,
         param_policy_fn=param_policy_fn,
         process_group_policy=process_group_policy,
+        comm_backend=comm_backend,
     )
 
 
@@ -453,7 +481,7 @@ def dedicate_params_ddp(
     """Replicated (DDP-style) placement: every rank keeps the live parameter,
     gradients are reduced to the owner, the owner's update is broadcast after
     the step.  Use together with :func:`replicate` for the other parameters."""
-    if mesh.ndim != 1:
+    if getattr(mesh, "ndim", 1) != 1:
         raise ValueError("dedicate_params_ddp expects a 1-D data-parallel mesh")
     return _setup(
         model,
@@ -499,7 +527,7 @@ def dedicate_params_ddp_tp(
 ) -> dict:
     """Replicated placement for models whose matrices are DTensors sharded on a
     tensor-parallel mesh dimension (``mesh`` is the data-parallel dimension)."""
-    if mesh.ndim != 1:
+    if getattr(mesh, "ndim", 1) != 1:
         raise ValueError("dedicate_params_ddp_tp expects the 1-D data-parallel sub-mesh")
     out = _setup(
         model,

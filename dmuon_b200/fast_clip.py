@@ -183,8 +183,8 @@ def try_clip_optimizer_grad_norm_buckets_(
     ensure = getattr(optimizer, "_ensure_grads_ready", None)
     if ensure is None or not hasattr(optimizer, "owned_muon_params"):
         return None
-    ensure()
-    muon = [e.grad for e in iter_muon_grad_entries(optimizer)]
+    ensure(materialize=True)
+    muon =[e.grad for e in iter_muon_grad_entries(optimizer)]
     res = clip_grad_norm_buckets_(
         (
             GradClipBucket("regular", regular_grads, reduce=False),

@@ -177,7 +177,7 @@ def clip_grad_norm_(
     all-reduce spans the world), owners and non-owners alike."""
     if not hasattr(optimizer, "_ensure_grads_ready") or not hasattr(optimizer, "owned_muon_params"):
         raise TypeError("clip_grad_norm_ expects a dmuon_b200.Muon optimizer")
-    optimizer._ensure_grads_ready()
+    optimizer._ensure_grads_ready(materialize=True)
     if isinstance(strategy, str):
         if strategy not in _STRATEGIES:
             raise ValueError(f"unknown Muon grad clip strategy {strategy!r}; registered: {sorted(_STRATEGIES)}")

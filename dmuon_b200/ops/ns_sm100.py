@@ -292,6 +292,7 @@ def muon_update_batched(
     publish: Optional[Sequence[torch.Tensor]] = None,
     deltas: Optional[Sequence[torch.Tensor]] = None,
     gscale: Optional[torch.Tensor] = None,
+    peer=None,
 ) -> None:
     """Momentum, Newton-Schulz and the weight update for ``L`` same-shape
     matrices.
@@ -302,13 +303,24 @@ def muon_update_batched(
     pre-scaled update ``-lr*update_scale*NS(u)`` is written there (fp32) and no
     weight is touched (tensor-parallel owners scatter it).
     """
-    L = len(grads)
+    L = len(moms)
     if L == 0:
         return
-    g0 = grads[0]
-    m0 = g0.shape[0]
-    n0 = g0.numel() // m0
-    dev = g0.device
+    m0, n0 = int(moms[0].shape[0]), int(moms[0].numel() // moms[0].shape[0])
+    dev = moms[0].device
+
+    def prologue(xs_out):
+        if peer is not None:
+            # reduce-to-owner fused into the prologue: gradients are read from
+            # every rank's arena through its peer mapping
+            from . import peer as P
+
+            P.peer_prologue(peer.peer_bases, peer.offsets, peer.numels, peer.grad_dtype, moms, xs_out, slots,
+                            ws.sumsq, scale=peer.scale, mu=mu, nesterov=nesterov, gscale=gscale,
+                            ready_flags=peer.ready_flags, ready_want=peer.ready_want, status=peer.status)
+        else:
+            MT.muon_prologue(grads, moms, xs_out, slots, ws.sumsq, mu, nesterov, gscale)
+
     cd = _resolve_dtype(compute_dtype, formulation)
     ws = workspace(L, m0, n0, cd, dev)
     left = m0 <= n0
@@ -316,7 +328,7 @@ def muon_update_batched(
     slots = list(range(L))
     if cd == torch.bfloat16 and formulation == "gram":
         # one pass: the raw bf16 operand carries its scale as a per-matrix vector
-        MT.muon_prologue(grads, moms, [ws.X[i] for i in range(L)], slots, ws.sumsq, mu, nesterov, gscale)
+        prologue([ws.X[i].reshape(-1) for i in range(L)])
         MT.norm_scales(ws.sumsq, ws.scale, ws.scale2, eps)
         xscale = _XScale(vec=ws.scale, vec2=ws.scale2)
     else:
@@ -324,7 +336,7 @@ def muon_update_batched(
         if ws.Xf32 is None:
             ws.Xf32 = torch.empty(L, m0, n0, device=dev, dtype=torch.float32)
         stage = [ws.Xf32[i] for i in range(L)]
-        MT.muon_prologue(grads, moms, stage, slots, ws.sumsq, mu, nesterov, gscale)
+        prologue([t.reshape(-1) for t in stage])
         MT.norm_scales(ws.sumsq, ws.scale, ws.scale2, eps)
         K = fp16_prescale(m0, n0) if (cd == torch.float16 and formulation == "gram") else 1.0
         if K != 1.0:

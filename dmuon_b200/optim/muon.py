@@ -389,8 +389,11 @@ class Muon(torch.optim.Optimizer):
         groups = self._comm_groups
         gscale, self._pending_gscale = self._pending_gscale, None
 
+        rt = getattr(self.comm_ctx, "peer_runtime", None)
         with prof.phase("prepare_muon_grads"):
             self._ensure_grads_ready()
+            if rt is not None:
+                rt.before_owner_writes()
         # a published copy that survived until here (evaluation forward, no
         # backward) would be stale after the update below
         for g in groups:
@@ -406,6 +409,9 @@ class Muon(torch.optim.Optimizer):
                 if not pg["use_muon"]:
                     self._step_dedicated_adamw(gi, pg, gscale)
         with prof.phase("post_step_publish"):
+            if rt is not None:
+                rt.after_optimizer_consumed()
+                rt.publish_owned()
             for g in groups:
                 g.post_step_publish_async()
             if not self.replicate_async or self._has_tp:
@@ -424,8 +430,13 @@ class Muon(torch.optim.Optimizer):
         self._last_profile = prof if self.record_step_profile else None
         return loss
 
-    def _ensure_grads_ready(self) -> None:
+    def _ensure_grads_ready(self, materialize: bool = False) -> None:
         prepare_muon_grads(self.model, coalesce_wait=True)
+        rt = getattr(self.comm_ctx, "peer_runtime", None)
+        if rt is not None:
+            rt.announce_grads()
+            if materialize:
+                rt.materialize([dp for dp in self._all_dedicated if dp.is_owner])
 
     # ------------------------------------------------------------------ Muon
     def _momentum_of(self, dp, shape, device) -> torch.Tensor:
@@ -449,13 +460,17 @@ class Muon(torch.optim.Optimizer):
                     continue
                 grad = dp._tp_full_grad
             else:
-                if dp._reduced_grad is None:
+                if dp._reduced_grad is None and not getattr(dp, "_peer_grad_pending", False):
                     continue
-                grad = dp._reduced_grad
+                grad = dp._reduced_grad      # None: still in the peers' arenas
             work.append((dp, grad))
         if not work:
             return
-        use_kernels = self.ns.uses_kernels(work[0][1])
+        use_kernels = self.device.type == "cuda" and self.ns.uses_kernels(work[0][0]._owned_data)
+        if not use_kernels and any(g is None for _, g in work):
+            rt = self.comm_ctx.peer_runtime
+            rt.materialize([dp for dp, g in work if g is None])
+            work = [(dp, dp._reduced_grad) for dp, _ in work]
         if use_kernels:
             self._step_muon_kernels(work, lr, mu, wd, gscale)
         else:
@@ -488,25 +503,35 @@ class Muon(torch.optim.Optimizer):
         from ..ops import ns_sm100
 
         by_shape: dict[tuple, list] = defaultdict(list)
+        rt = getattr(self.comm_ctx, "peer_runtime", None)
         for dp, grad in work:
-            rows = int(grad.shape[0])
-            key = (rows, grad.numel() // rows, grad.dtype, dp._optim_dtype, dp._owned_data.dtype, dp.tp_group is not None)
+            shape = grad.shape if grad is not None else dp._orig_size
+            rows = int(shape[0])
+            numel = grad.numel() if grad is not None else dp.numel
+            gdt = grad.dtype if grad is not None else "peer"
+            key = (rows, numel // rows, gdt, dp._optim_dtype, dp._owned_data.dtype, dp.tp_group is not None)
             by_shape[key].append((dp, grad))
         coefs = self.ns.resolved_coefficients(self.ns_steps)
         restarts = self.ns.resolved_restarts()
-        for (rows, cols, _gd, _od, _md, is_tp), items in by_shape.items():
+        for (rows, cols, gdt, _od, _md, is_tp), items in by_shape.items():
             cap = ns_sm100.max_batch(rows, cols)
             for lo in range(0, len(items), cap):
                 chunk = items[lo : lo + cap]
-                grads = [g.reshape(rows, cols) if g.is_contiguous() else g.reshape(rows, cols).contiguous() for _, g in chunk]
-                moms = [self._momentum_of(dp, (rows, cols), g.device) for dp, g in chunk]
+                moms = [self._momentum_of(dp, (rows, cols), self.device) for dp, _ in chunk]
+                if gdt == "peer":
+                    # reduce-to-owner happens inside the prologue kernel
+                    grads = None
+                    peer = rt.source_for([dp for dp, _ in chunk])
+                else:
+                    peer = None
+                    grads = [g.reshape(rows, cols) if g.is_contiguous() else g.reshape(rows, cols).contiguous() for _, g in chunk]
                 common = dict(
                     mu=mu, nesterov=self.nesterov, coefs=coefs, restarts=restarts, formulation=self.ns.backend,
                     lr=lr, weight_decay=wd, update_scale=muon_update_scale((rows, cols)),
-                    compute_dtype=self.ns.compute_dtype, gscale=gscale,
+                    compute_dtype=self.ns.compute_dtype, gscale=gscale, peer=peer,
                 )
                 if is_tp:
-                    deltas = [torch.empty(dp.full_shape, dtype=torch.float32, device=g.device) for dp, g in chunk]
+                    deltas = [torch.empty(dp.full_shape, dtype=torch.float32, device=self.device) for dp, _ in chunk]
                     ns_sm100.muon_update_batched(grads, moms, None, deltas=deltas, **common)
                     for (dp, _), d in zip(chunk, deltas):
                         dp._tp_full_delta = d
@@ -576,6 +601,9 @@ class Muon(torch.optim.Optimizer):
 
     def _step_dedicated_adamw(self, gi: int, pg: dict, gscale) -> None:
         entries = []
+        rt = getattr(self.comm_ctx, "peer_runtime", None)
+        if rt is not None:
+            rt.materialize(list(self._bucket_dps.get(gi, ())))
         for dp in self._bucket_dps.get(gi, ()):
             if dp._dmuon_route == "sharded_adamw":
                 g, p = dp._sharded_adamw_grad, dp._sharded_adamw_data
@@ -612,6 +640,7 @@ class Muon(torch.optim.Optimizer):
             dp._sharded_adamw_grad = None
             dp._accumulated_grad = None
             dp._tp_full_grad = None
+            dp._peer_grad_pending = False
             if dp.mode == "ddp":
                 dp.clear_local_grad()
         for p in self._plain_params:

@@ -1,0 +1,146 @@
+"""Peer-memory kernels.  On one GPU the "ranks" are emulated as one kernel
+reading several local arenas; with two or more GPUs the whole data plane is
+compared against the NCCL implementation."""
+import pytest
+import torch
+
+from dist_utils import run_ranks
+
+pytestmark = pytest.mark.gpu
+
+
+def test_peer_prologue_reduces_in_rank_order_and_applies_momentum():
+    from dmuon_b200.ops import peer as P
+
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    W = 4
+    sizes = [1024 * 3 + 8, 4096, 40]
+    offs, total = [], 0
+    for n in sizes:
+        offs.append(total)
+        total += (n + 63) // 64 * 64
+    arenas = [torch.randn(total, device=dev).bfloat16() for _ in range(W)]
+    moms = [torch.randn(n, device=dev) for n in sizes]
+    m0 = [m.clone() for m in moms]
+    xs = [torch.empty(n, device=dev, dtype=torch.bfloat16) for n in sizes]
+    sumsq = torch.zeros(3, device=dev)
+    flags = torch.full((8,), 5, dtype=torch.int32, device=dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    P.peer_prologue([a.data_ptr() for a in arenas], offs, sizes, torch.bfloat16, moms, xs, [0, 1, 2], sumsq,
+                    scale=1.0 / W, mu=0.95, nesterov=True, ready_flags=flags, ready_want=5, status=status)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
+    for i, n in enumerate(sizes):
+        g = torch.zeros(n, device=dev)
+        for a in arenas:                       # same order as the kernel
+            g = g + a[offs[i] : offs[i] + n].float()
+        g = g / W
+        m = 0.95 * m0[i] + g
+        u = g + 0.95 * m
+        assert torch.allclose(moms[i], m, atol=1e-5)
+        assert (xs[i].float() - u).abs().max().item() < 0.02 * u.abs().max().item()
+        assert abs(sumsq[i].item() - float((u * u).sum())) < 1e-3 * float((u * u).sum())
+    # reduce only (no momentum): fp32 result
+    outs = [torch.empty(n, device=dev) for n in sizes]
+    P.peer_prologue([a.data_ptr() for a in arenas], offs, sizes, torch.bfloat16, [None] * 3, outs, [0, 0, 0], None,
+                    scale=1.0 / W, mu=0.0, nesterov=False)
+    torch.cuda.synchronize()
+    for i, n in enumerate(sizes):
+        g = sum(a[offs[i] : offs[i] + n].float() for a in arenas) / W
+        assert torch.allclose(outs[i], g, atol=1e-5)
+
+
+def test_pull_and_signal_on_one_device():
+    from dmuon_b200.ops import peer as P
+
+    dev = torch.device("cuda", 0)
+    src = torch.randn(1 << 20, device=dev).bfloat16()
+    dst = torch.zeros_like(src)
+    flags = torch.zeros(32, dtype=torch.int32, device=dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    P.signal_peers([flags.data_ptr()], 3, 7, dev)            # "owner" announces epoch 7 in slot 3
+    P.peer_pull([src.data_ptr()], [dst.data_ptr()], [src.numel() * 2], [3], flags, 7, status, dev)
+    torch.cuda.synchronize()
+    assert int(flags[3]) == 7 and int(status[0]) == 0
+    assert torch.equal(src, dst)
+
+
+def test_flag_wait_times_out_cleanly():
+    """A flag nobody sets: the wait gives up after its budget, reports status 4
+    and the context stays usable."""
+    from dmuon_b200.ops import peer as P
+
+    dev = torch.device("cuda", 0)
+    flags = torch.zeros(8, dtype=torch.int32, device=dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    P.wait_flags(flags, 0, 2, 1, status, budget_cycles=20_000_000)      # ~10 ms
+    torch.cuda.synchronize()
+    assert int(status[0]) == 4
+    status.zero_()
+    out = torch.empty(64, device=dev)
+    P.peer_prologue([flags.data_ptr()], [0], [8], torch.float32, [None], [out[:8]], [0], None, scale=1.0, mu=0.0,
+                    nesterov=False, ready_flags=flags, ready_want=9, status=status, budget_cycles=20_000_000)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 4
+    assert float((torch.ones(4, device=dev) * 2).sum()) == 8.0
+
+
+def _train_body(rank, world, backend, steps):
+    import torch.distributed as dist
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
+
+    import dmuon_b200 as dmuon
+    from dmuon_b200.models.llama import LlamaConfig, LlamaModel
+
+    dev = torch.device("cuda", rank)
+    cfg = LlamaConfig(vocab_size=2048, d_model=512, n_layers=3, n_heads=8, n_kv_heads=4, head_dim=64,
+                      ffn_hidden=1536, rope_theta=10000.0)
+    torch.manual_seed(0)
+    with torch.device(dev):
+        model = LlamaModel(cfg)
+    mesh = init_device_mesh("cuda", (world,), mesh_dim_names=("dp",))
+    dmuon.dedicate_params(model, mesh, lambda n, p: "proj" in n and p.ndim == 2, compute_dtype=torch.bfloat16,
+                          reshard_after_forward=False, comm_backend=backend)
+    mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
+    for layer in model.layers:
+        fully_shard(layer, mesh=mesh, mp_policy=mp)
+    fully_shard(model, mesh=mesh, mp_policy=mp)
+    opt = dmuon.Muon(model, lr=0.02, adamw_lr=1e-3, weight_decay=0.1)
+    used_peer = model._dedicated_comm_ctx.peer_runtime is not None
+    g = torch.Generator().manual_seed(100 + rank)
+    losses = []
+    for s in range(steps):
+        ids = torch.randint(0, cfg.vocab_size, (2, 129), generator=g).to(dev)
+        opt.zero_grad()
+        if s == 1:                      # one accumulation step with two micro-batches
+            (model(ids[:1, :-1], labels=ids[:1, 1:]) / 2).backward()
+            loss = model(ids[1:, :-1], labels=ids[1:, 1:]) / 2
+        else:
+            loss = model(ids[:, :-1], labels=ids[:, 1:])
+        loss.backward()
+        if s == 2:
+            dmuon.clip_grad_norm_(opt, 0.5)
+        opt.step()
+        lt = loss.detach().float().clone()
+        dist.all_reduce(lt)
+        losses.append(float(lt) / world)
+    if used_peer:
+        model._dedicated_comm_ctx.peer_runtime.check()
+    sd = dmuon.get_model_state_dict(model, rank0_only=False)
+    return losses, {k: v for k, v in sd.items() if "proj" in k}, used_peer
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_peer_data_plane_matches_nccl():
+    world = min(4, torch.cuda.device_count())
+    steps = 4
+    ref = run_ranks(_train_body, world, args=("nccl", steps), backend="nccl", timeout=600)
+    got = run_ranks(_train_body, world, args=("peer", steps), backend="nccl", timeout=600)
+    assert not ref[0][2] and got[0][2]
+    for a, b in zip(got[0][0], ref[0][0]):
+        assert abs(a - b) < 2e-2 * max(1.0, abs(b)), (got[0][0], ref[0][0])
+    for k, v in ref[0][1].items():
+        d = (got[0][1][k].float() - v.float()).abs().max().item()
+        assert d < 5e-2 * (v.float().abs().max().item() + 1e-3), (k, d)

@@ -32,7 +32,20 @@ MODELS = {
     "llama3.2-3b": (3072, 28, 24, 8, 128, 8192, 128256, 4096, 2),
     "llama-1b": (2048, 16, 32, 8, 64, 8192, 128256, 4096, 2),
     "tiny": (256, 4, 4, 4, 64, 1024, 1024, 128, 4),
+    # Pi0-style VLA (vision tower + Gemma-2B-shaped backbone + action expert); "seq" is the
+    # token count per sample (3 x 256 image tokens + 48 prompt + 51 action tokens), batch 32 per GPU
+    "pi0": (2048, 18, 8, 1, 256, 16384, 257152, 867, 32),
 }
+
+
+def pi0_host_batch(dims, mb, gen):
+    import torch
+
+    images = torch.rand(mb, 3, 3, 224, 224, generator=gen) * 2 - 1
+    prompt = torch.randint(0, dims["vocab_size"], (mb, 48), generator=gen)
+    state = torch.randn(mb, 32, generator=gen)
+    actions = torch.randn(mb, 50, 32, generator=gen)
+    return images.to(torch.bfloat16), prompt, state, actions
 
 
 def parse_args():
@@ -170,6 +183,8 @@ def build_ours(args, dims, rank, world, device):
     from dmuon_b200.models.llama import LlamaConfig, LlamaModel
 
     llama_mod.ATTENTION_BACKEND = args.attention
+    if args.model == "pi0":
+        return build_ours_pi0(args, dims, rank, world, device)
     cfg = LlamaConfig(
         vocab_size=dims["vocab_size"], d_model=dims["d_model"], n_layers=dims["n_layers"], n_heads=dims["n_heads"],
         n_kv_heads=dims["n_kv_heads"], head_dim=dims["head_dim"], ffn_hidden=dims["ffn_hidden"], rope_theta=500000.0,
@@ -210,8 +225,52 @@ def build_ours(args, dims, rank, world, device):
         fully_shard(model, mesh=fsdp_mesh, mp_policy=mp)
         opt = torch.optim.AdamW(model.parameters(), lr=1e-3, weight_decay=0.01, fused=True)
 
-    def fwd_bwd(ids, labels):
-        loss = model(ids, labels=labels)
+    def fwd_bwd(b):
+        loss = model(b[:, :-1], labels=b[:, 1:])
+        loss.backward()
+        return loss
+
+    def launches():
+        from dmuon_b200.ops import multi_tensor as MT
+
+        return MT.launch_count()
+
+    ctx = getattr(model, "_dedicated_comm_ctx", None)
+    args.comm_used = "peer-memory kernels" if getattr(ctx, "peer_runtime", None) is not None else "nccl"
+    return fwd_bwd, opt, launches
+
+
+def build_ours_pi0(args, dims, rank, world, device):
+    import torch
+    from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
+
+    import dmuon_b200 as dmuon
+    from dmuon_b200.models.pi0 import Pi0Config, Pi0Model
+
+    cfg = Pi0Config()
+    torch.manual_seed(42)
+    with torch.device(device):
+        model = Pi0Model(cfg)
+    mesh_all, shard_mesh, rep_mesh = make_mesh(args, world)
+    mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.bfloat16)
+    blocks = list(model.vision.blocks) + list(model.layers)
+    if args.optimizer == "muon":
+        dmuon.dedicate_params(model, shard_mesh, _pred, compute_dtype=torch.bfloat16,
+                              reshard_after_forward=args.reshard_after_forward, replicate_mesh=rep_mesh,
+                              comm_backend=args.comm)
+        for blk in blocks:
+            fully_shard(blk, mesh=mesh_all, mp_policy=mp)
+        fully_shard(model, mesh=mesh_all, mp_policy=mp)
+        opt = dmuon.Muon(model, lr=0.02, ns_steps=5, adamw_lr=1e-3, weight_decay=0.1,
+                         ns_backend=dmuon.NewtonSchulz(backend=args.ns))
+    else:
+        for blk in blocks:
+            fully_shard(blk, mesh=mesh_all, mp_policy=mp)
+        fully_shard(model, mesh=mesh_all, mp_policy=mp)
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-3, weight_decay=0.01, fused=True)
+
+    def fwd_bwd(images, prompt, state, actions):
+        loss = model(images, prompt, state, actions)
         loss.backward()
         return loss
 
@@ -226,6 +285,8 @@ def build_ours(args, dims, rank, world, device):
 
 
 def build_reference(args, dims, rank, world, device):
+    if args.model == "pi0":
+        raise RuntimeError("the reference ships no vision-language-action model to run this configuration with")
     """The unmodified reference installed under baseline/_ref, driven through
     its public API the way its own LLM benchmark does (Hugging Face Llama,
     dedicate_params -> fully_shard -> Muon)."""
@@ -267,8 +328,8 @@ def build_reference(args, dims, rank, world, device):
         fully_shard(model, mesh=mesh_all, mp_policy=mp)
         opt = torch.optim.AdamW(model.parameters(), lr=1e-3, weight_decay=0.01, fused=True)
 
-    def fwd_bwd(ids, labels):
-        out = model(input_ids=ids, labels=labels)
+    def fwd_bwd(b):
+        out = model(input_ids=b[:, :-1], labels=b[:, 1:])
         out.loss.backward()
         return out.loss
 
@@ -288,19 +349,21 @@ def run(args):
 
     gen = torch.Generator().manual_seed(1234 + rank)
     n_batches = 4
-    host = [torch.randint(0, vocab, (mb, seq + 1), generator=gen).pin_memory() for _ in range(n_batches)]
-    dev_batches = [h.to(device) for h in host]
+    if args.model == "pi0":
+        host = [tuple(t.pin_memory() for t in pi0_host_batch(dims, mb, gen)) for _ in range(n_batches)]
+    else:
+        host = [(torch.randint(0, vocab, (mb, seq + 1), generator=gen).pin_memory(),) for _ in range(n_batches)]
+    dev_batches = [tuple(t.to(device) for t in h) for h in host]
+    h2d_bytes = sum(t.numel() * t.element_size() for t in host[0])
 
     def step_device(i):
-        b = dev_batches[i % n_batches]
         opt.zero_grad()
-        loss = fwd_bwd(b[:, :-1], b[:, 1:])
-        return loss
+        return fwd_bwd(*dev_batches[i % n_batches])
 
     def step_e2e(i):
-        b = host[i % n_batches].to(device, non_blocking=True)
+        b = tuple(t.to(device, non_blocking=True) for t in host[i % n_batches])
         opt.zero_grad()
-        loss = fwd_bwd(b[:, :-1], b[:, 1:])
+        loss = fwd_bwd(*b)
         opt.step()
         return float(loss.item())          # device -> host read of the step's result
 
@@ -390,7 +453,7 @@ def run(args):
                 "value": round(e2e_max, 3),
                 "unit": "ms/step",
                 "tokens_per_s": round(tokens / (e2e_max / 1e3), 1),
-                "h2d_bytes_per_step": int(mb * (seq + 1) * 8),
+                "h2d_bytes_per_step": int(h2d_bytes),
                 "d2h_bytes_per_step": 4,
             }
         print(json.dumps(out), flush=True)

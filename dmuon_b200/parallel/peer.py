@@ -110,10 +110,6 @@ class PeerRuntime:
         self.grad.zero_()
         torch.cuda.synchronize(self.device)
         name = dp_group.group_name
-        try:
-            symm_mem.enable_symm_mem_for_group(name)
-        except Exception:  # newer torch versions enable groups on demand
-            pass
         self.pub_hdl = symm_mem.rendezvous(self.pub, name)
         self.grad_hdl = symm_mem.rendezvous(self.grad, name)
         self.flag_hdl = symm_mem.rendezvous(self.flags, name)

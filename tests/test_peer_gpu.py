@@ -101,7 +101,10 @@ def _train_body(rank, world, backend, steps):
     with torch.device(dev):
         model = LlamaModel(cfg)
     mesh = init_device_mesh("cuda", (world,), mesh_dim_names=("dp",))
-    dmuon.dedicate_params(model, mesh, lambda n, p: "proj" in n and p.ndim == 2, compute_dtype=torch.bfloat16,
+    # fp32 gradient buffers on both data planes: with two ranks the sum is then the
+    # same number whoever computes it, so the trajectories can be compared tightly
+    dmuon.dedicate_params(model, mesh, lambda n, p: "proj" in n and p.ndim == 2,
+                          param_policy={"defaults": {"param_dtype": "bf16", "grad_dtype": "fp32"}},
                           reshard_after_forward=False, comm_backend=backend)
     mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
     for layer in model.layers:
@@ -134,13 +137,71 @@ def _train_body(rank, world, backend, steps):
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_peer_data_plane_matches_nccl():
-    world = min(4, torch.cuda.device_count())
+    world = 2
     steps = 4
     ref = run_ranks(_train_body, world, args=("nccl", steps), backend="nccl", timeout=600)
     got = run_ranks(_train_body, world, args=("peer", steps), backend="nccl", timeout=600)
     assert not ref[0][2] and got[0][2]
     for a, b in zip(got[0][0], ref[0][0]):
         assert abs(a - b) < 2e-2 * max(1.0, abs(b)), (got[0][0], ref[0][0])
+    # Newton-Schulz amplifies rounding differences along weak singular directions,
+    # so compare in the Frobenius norm rather than element by element
     for k, v in ref[0][1].items():
-        d = (got[0][1][k].float() - v.float()).abs().max().item()
-        assert d < 5e-2 * (v.float().abs().max().item() + 1e-3), (k, d)
+        rel = (got[0][1][k].float() - v.float()).norm().item() / (v.float().norm().item() + 1e-12)
+        assert rel < 5e-3, (k, rel)
+
+
+def _reduce_check_body(rank, world):
+    import torch.distributed as dist
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+    from dmuon_b200.models.llama import LlamaConfig, LlamaModel
+
+    dev = torch.device("cuda", rank)
+    cfg = LlamaConfig(vocab_size=512, d_model=256, n_layers=2, n_heads=4, n_kv_heads=4, head_dim=64,
+                      ffn_hidden=512, rope_theta=10000.0)
+    torch.manual_seed(0)
+    with torch.device(dev):
+        model = LlamaModel(cfg).bfloat16()
+    mesh = init_device_mesh("cuda", (world,), mesh_dim_names=("dp",))
+    dmuon.dedicate_params(model, mesh, lambda n, p: "proj" in n and p.ndim == 2, comm_backend="peer")
+    for layer in model.layers:
+        fully_shard(layer, mesh=mesh)
+    fully_shard(model, mesh=mesh)
+    opt = dmuon.Muon(model, lr=0.02)
+    rt = model._dedicated_comm_ctx.peer_runtime
+    worst = 0.0
+    for step in range(2):
+        g = torch.Generator().manual_seed(7 + rank + 10 * step)
+        ids = torch.randint(0, cfg.vocab_size, (2, 65), generator=g).to(dev)
+        opt.zero_grad()
+        model(ids[:, :-1], labels=ids[:, 1:]).backward()
+        # what an all-reduce of the local arenas would give
+        want = {}
+        for dp in dmuon.get_dedicated_params(model):
+            t = dp._grad_view.float().clone()
+            dist.all_reduce(t)
+            want[dp.fqn] = t / world
+        opt._ensure_grads_ready(materialize=True)
+        for dp in dmuon.get_owned_params(model):
+            got = dp._reduced_grad
+            worst = max(worst, (got - want[dp.fqn]).abs().max().item() / (want[dp.fqn].abs().max().item() + 1e-12))
+        # published weights: every rank's copy equals the owner's master weights in bf16
+        opt.step()
+        model(ids[:, :-1])                       # forward pulls the new epoch
+        torch.cuda.synchronize()
+        for dp in dmuon.get_dedicated_params(model):
+            ref = dp._owned_data.to(torch.bfloat16) if dp.is_owner else torch.empty(dp._orig_size, dtype=torch.bfloat16, device=dev)
+            dist.broadcast(ref, src=dp.owner_shard)
+            assert torch.equal(dp._unsharded_param.data, ref), dp.fqn
+    rt.check()
+    return worst
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_peer_reduce_and_publish_are_exact():
+    world = min(4, torch.cuda.device_count())
+    worst = run_ranks(_reduce_check_body, world, backend="nccl", timeout=600)
+    assert max(worst) < 1e-5, worst

@@ -274,8 +274,12 @@ static int blocks_per_tensor(int ntensors, const long long* numel) {
   long long mx = 0;
   for (int i = 0; i < ntensors; ++i) mx = numel[i] > mx ? numel[i] : mx;
   long long need = (mx + static_cast<long long>(kBlock) * kVec - 1) / (static_cast<long long>(kBlock) * kVec);
-  long long cap = (148LL * 8 + ntensors - 1) / ntensors;   // about 8 resident blocks per SM overall
-  if (cap < 1) cap = 1;
+  // About 8 resident blocks per SM overall when the tensors are alike, but never
+  // fewer than 4 per SM for one row: a launch that mixes one huge tensor with
+  // many small ones (embedding + norms) must still fill the GPU for the huge
+  // one; surplus blocks of small rows exit at once.
+  long long cap = (148LL * 8 + ntensors - 1) / ntensors;
+  if (cap < 148LL * 4) cap = 148LL * 4;
   long long b = need < cap ? need : cap;
   return static_cast<int>(b < 1 ? 1 : b);
 }

@@ -217,7 +217,7 @@ static int grid_x(long long max_items, int ntensors, int override_blocks) {
   if (override_blocks > 0) return override_blocks;
   long long need = (max_items + kBlock - 1) / kBlock;
   long long cap = (148LL * 4 + ntensors - 1) / ntensors;
-  if (cap < 1) cap = 1;
+  if (cap < 148LL * 2) cap = 148LL * 2;
   long long b = need < cap ? need : cap;
   return static_cast<int>(b < 1 ? 1 : b);
 }

@@ -512,3 +512,156 @@ extern "C" int dmuon_gemm_sm100(const DmuonGemmArgs* args, void* stream_v) {
   if (a.bn == 256) return launch<256>(a, tmA, tmB, stream, sms);
   return launch<128>(a, tmA, tmB, stream, sms);
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free symmetric product (see noalloc.cuh).  Same kernel as above;
+// its tile table and status word live in a static device array instead of
+// caller-provided memory.
+// ---------------------------------------------------------------------------
+#include "noalloc.cuh"
+
+namespace dmuon {
+
+// [0, 256): header, word 0 = status.  [256, ...): tile table (int4 per tile).
+static __device__ __align__(256) unsigned char g_noalloc_scratch[DMUON_NOALLOC_SCRATCH_BYTES];
+
+// Device code may name the array directly: one thread enumerates the tiles
+// that touch the lower triangle, row tile by row tile.
+__global__ void noalloc_fill_tiles_kernel(int M, int bn) {
+  if (blockIdx.x != 0 || threadIdx.x != 0) return;
+  int4* tab = reinterpret_cast<int4*>(g_noalloc_scratch + DMUON_NOALLOC_HEADER_BYTES);
+  const int mt = (M + BM - 1) / BM;
+  int n = 0;
+  for (int i = 0; i < mt; ++i) {
+    const int last_row = min(M, (i + 1) * BM) - 1;
+    for (int j = 0; j <= last_row / bn; ++j) {
+      const int mirror = ((j + 1) * bn <= i * BM) ? 1 : 0;
+      tab[n++] = make_int4(i, j, mirror, 0);
+    }
+  }
+}
+
+static int noalloc_tile_count(int M, int bn) {
+  const int mt = (M + BM - 1) / BM;
+  long long n = 0;
+  for (int i = 0; i < mt; ++i) {
+    const int last_row = (M < (i + 1) * BM ? M : (i + 1) * BM) - 1;
+    n += last_row / bn + 1;
+  }
+  return n > 0x7fffffff ? 0x7fffffff : static_cast<int>(n);
+}
+
+// Host code must not pass `g_noalloc_scratch` itself to a kernel: in host code
+// that name is only a stand-in.  The device address is looked up once per
+// device, with that device current.
+static unsigned char* noalloc_scratch_ptr(int* err) {
+  static unsigned char* ptrs[16] = {};
+  static std::mutex mu;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 16) {
+    *err = DMUON_NOALLOC_E_SYMBOL;
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      *err = DMUON_NOALLOC_E_SYMBOL;
+      return nullptr;
+    }
+    ptrs[dev] = static_cast<unsigned char*>(p);
+  }
+  return ptrs[dev];
+}
+
+}  // namespace dmuon
+
+extern "C" int dmuon_syrk_noalloc(const void* X, void* D, int M, int K, int batch, long long ldx, long long ldd,
+                                  long long strideX, long long strideD, int is_fp16, int x_mn_major, float alpha,
+                                  float diag, void* stream_v) {
+  using namespace dmuon;
+  if (X == nullptr || D == nullptr || M <= 0 || K <= 0 || batch <= 0) return DMUON_NOALLOC_E_BAD_ARGUMENT;
+  if ((ldx % 8) != 0 || (ldd % 8) != 0 || (strideX % 8) != 0 || (strideD % 8) != 0)
+    return DMUON_NOALLOC_E_BAD_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(X) & 15) || (reinterpret_cast<uintptr_t>(D) & 15))
+    return DMUON_NOALLOC_E_BAD_ARGUMENT;
+  const int bn = (M <= 128) ? 128 : 256;
+  const int ntiles = noalloc_tile_count(M, bn);
+  if (ntiles > DMUON_NOALLOC_MAX_TILES) return DMUON_NOALLOC_E_TOO_LARGE;
+  int err = 0;
+  unsigned char* scratch = noalloc_scratch_ptr(&err);
+  if (scratch == nullptr) return err;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+
+  // the array keeps the previous call's contents: clear the header, rewrite the table
+  cudaError_t ce = cudaMemsetAsync(scratch, 0, DMUON_NOALLOC_HEADER_BYTES, stream);
+  if (ce != cudaSuccess) return static_cast<int>(ce);
+  noalloc_fill_tiles_kernel<<<1, 32, 0, stream>>>(M, bn);
+  count_launch();
+  ce = cudaGetLastError();
+  if (ce != cudaSuccess) return static_cast<int>(ce);
+
+  DmuonGemmArgs a = {};
+  a.A = X;
+  a.B = X;
+  a.lda = a.ldb = ldx;
+  a.strideA = a.strideB = strideX;
+  a.a_mn_major = a.b_mn_major = x_mn_major ? 1 : 0;
+  a.ab_fp16 = is_fp16 ? 1 : 0;
+  a.M = a.N = M;
+  a.K = K;
+  a.batch = batch;
+  a.tile_tab = reinterpret_cast<const int*>(scratch + DMUON_NOALLOC_HEADER_BYTES);
+  a.tiles_per_batch = ntiles;
+  a.bn = bn;
+  a.alpha = alpha;
+  a.beta = 0.f;
+  a.diag = diag;
+  a.D = D;
+  a.ldd = ldd;
+  a.strideD = strideD;
+  a.out_kind = is_fp16 ? 1 : 0;
+  a.status = reinterpret_cast<int*>(scratch);
+
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!a.a_mn_major) {
+    rc = make_map(&tmA, a.A, a.ab_fp16 != 0, a.K, a.M, a.batch, a.lda, a.strideA, BK, BM);
+    if (rc == 0) rc = make_map(&tmB, a.B, a.ab_fp16 != 0, a.K, a.N, a.batch, a.ldb, a.strideB, BK, bn);
+  } else {
+    rc = make_map(&tmA, a.A, a.ab_fp16 != 0, a.M, a.K, a.batch, a.lda, a.strideA, 64, BK);
+    if (rc == 0) rc = make_map(&tmB, a.B, a.ab_fp16 != 0, a.N, a.K, a.batch, a.ldb, a.strideB, 64, BK);
+  }
+  if (rc != 0) return DMUON_NOALLOC_E_BAD_ARGUMENT;
+  return bn == 256 ? launch<256>(a, tmA, tmB, stream, sms) : launch<128>(a, tmA, tmB, stream, sms);
+}
+
+extern "C" int dmuon_syrk_noalloc_status(void* stream_v) {
+  using namespace dmuon;
+  int err = 0;
+  unsigned char* scratch = noalloc_scratch_ptr(&err);
+  if (scratch == nullptr) return err;
+  int status = 0;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  if (cudaMemcpyAsync(&status, scratch, sizeof(int), cudaMemcpyDeviceToHost, stream) != cudaSuccess) return -1;
+  if (cudaStreamSynchronize(stream) != cudaSuccess) return -1;
+  return status;
+}
+
+extern "C" const char* dmuon_syrk_noalloc_strerror(int code) {
+  switch (code) {
+    case DMUON_NOALLOC_OK: return "ok";
+    case DMUON_NOALLOC_E_BAD_ARGUMENT:
+      return "bad argument: null or misaligned pointer, non-positive size, or a pitch/stride that is not a multiple of 8 elements";
+    case DMUON_NOALLOC_E_TOO_LARGE:
+      return "problem too large for the built-in scratch array: more than 16384 output tiles per matrix (M above 32512)";
+    case DMUON_NOALLOC_E_SYMBOL: return "cudaGetSymbolAddress failed for the built-in scratch array on this device";
+    default: return code > 0 ? "CUDA error (cudaError_t value) from a launch or memset" : "unknown code";
+  }
+}

@@ -66,6 +66,8 @@ def parse_args():
     ap.add_argument("--momentum-dtype", choices=("fp32", "bf16"), default="fp32")
     ap.add_argument("--comm", choices=("auto", "peer", "nccl"), default="auto",
                     help="data plane for dedicated parameters (this package only)")
+    ap.add_argument("--fused-publish", action="store_true",
+                    help="pull each dedicated Linear weight inside its first forward GEMM (peer data plane only)")
     ap.add_argument("--attention", choices=("cudnn", "flash"), default="cudnn",
                     help="SDPA backend preference of this package's model (the reference arm uses Hugging Face's default)")
     return ap.parse_args()
@@ -183,6 +185,8 @@ def build_ours(args, dims, rank, world, device):
     from dmuon_b200.models.llama import LlamaConfig, LlamaModel
 
     llama_mod.ATTENTION_BACKEND = args.attention
+    if args.fused_publish:
+        os.environ["DMUON_FUSED_PUBLISH"] = "1"
     if args.model == "pi0":
         return build_ours_pi0(args, dims, rank, world, device)
     cfg = LlamaConfig(
@@ -442,7 +446,8 @@ def run(args):
                 "parallelism": (args.parallelism if args.parallelism != "fsdp" else f"fsdp{world}")
                 + ("-z3" if args.reshard_after_forward else "-z2"),
                 "newton_schulz": args.ns,
-                "dedicated_data_plane": getattr(args, "comm_used", "nccl"),
+                "dedicated_data_plane": getattr(args, "comm_used", "nccl")
+                + (" + publish fused into forward GEMMs" if args.fused_publish else ""),
                 "attention": (args.attention + " SDPA backend" if args.impl == "ours" else "Hugging Face sdpa default"),
                 "activation_checkpointing": bool(args.act_ckpt),
                 "l2": "per-step working set (weights + activations, tens of GB) is far larger than the 126 MB L2",

@@ -83,6 +83,25 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   }
 }
 
+// Same with a caller-chosen budget (kernels whose progress depends on another
+// GPU wait as long as the cross-GPU flag waits do).
+__device__ __forceinline__ bool mbar_wait_long(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                               long long budget_cycles) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > budget_cycles) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+
 // --- TMA (cp.async.bulk.tensor), 3-D tiled load, no multicast -------------
 __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const void* tmap, uint32_t bar,
                                             int c0, int c1, int c2) {
@@ -187,6 +206,48 @@ __device__ __forceinline__ uint32_t make_idesc_f16(int m, int n, bool ab_is_fp16
   d |= static_cast<uint32_t>(n >> 3) << 17;
   d |= static_cast<uint32_t>(m >> 4) << 24;
   return d;
+}
+
+// --- untiled bulk copies (16-byte aligned addresses, size a multiple of 16) ---
+// global (this GPU's or a peer's memory) -> shared, completion on an mbarrier
+__device__ __forceinline__ void bulk_load_g2s(uint32_t smem_dst, const void* gsrc, uint32_t bytes,
+                                              uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      :
+      : "r"(smem_dst), "l"(gsrc), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
+// shared -> global, tracked by the bulk async-group of the issuing thread
+__device__ __forceinline__ void bulk_store_s2g(void* gdst, uint32_t smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_src),
+               "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ void bulk_commit_group() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+// all but the newest `N` groups have finished READING their shared-memory source
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+
+// all but the newest `N` groups have completed (their global writes are done)
+template <int N>
+__device__ __forceinline__ void bulk_wait_group() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void fence_proxy_async_all() {
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
+
+__device__ __forceinline__ void red_add_release_gpu(int* p, int v) {
+  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 // --- peer / flag helpers ----------------------------------------------------

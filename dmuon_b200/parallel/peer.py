@@ -80,8 +80,33 @@ class PeerSource:
         self.status = rt.status
 
 
+def fused_forward_requested() -> bool:
+    return os.environ.get("DMUON_FUSED_PUBLISH", "0").strip().lower() in ("1", "true", "yes", "on")
+
+
+def _fused_linear_forward(self, x):
+    """``nn.Linear.forward`` replacement: the first use of the weight in a
+    publish epoch runs the kernel that pulls it from its owner while
+    multiplying; later uses (recompute, second micro-batch) read the local copy."""
+    import torch.nn.functional as F
+
+    rt, p = self._dmuon_fused
+    w = self.weight
+    if p._fused_epoch != rt.pub_epoch and w.numel() == p.numel:
+        from ..ops import pull_linear as PL
+
+        if PL.supported(x, w):
+            p._fused_epoch = rt.pub_epoch
+            remote, flag, want, budget = rt.fused_pull_args(p)
+            return PL.PulledLinearFn.apply(x, w, self.bias, remote, flag, want, budget)
+        # unsupported input this time: fetch the weight the ordinary way first
+        rt.pull_params([p])
+        p._fused_epoch = rt.pub_epoch
+    return F.linear(x, w, self.bias)
+
+
 class PeerRuntime:
-    def __init__(self, ctx, dp_group, groups: list["PeerParamGroup"]):
+    def __init__(self, ctx, dp_group, groups: list["PeerParamGroup"], fused_forward: Optional[bool] = None):
         import torch.distributed._symmetric_memory as symm_mem
 
         from ..ops import gemm as G
@@ -132,8 +157,42 @@ class PeerRuntime:
                 p._publish_view = view if p.is_owner else None
                 p._peer_grad_pending = False
         self._remote_groups = sum(1 for g in groups if any(s != self.rank for s in g._pub_by_shard))
+        self.fused_forward = fused_forward_requested() if fused_forward is None else bool(fused_forward)
+        if self.fused_forward:
+            self._install_fused_linears()
         dist.barrier(group=dp_group)
         self.publish_owned()
+
+    # ------------------------------------------------------------------ fused forward publish
+    def _install_fused_linears(self) -> None:
+        """Give every plain ``nn.Linear`` whose weight is a dedicated parameter
+        owned by ANOTHER rank a forward that pulls the weight inside its GEMM.
+        Anything else (shared weights, custom modules, direct ``.weight`` use)
+        keeps the pull-then-compute path."""
+        import types
+
+        import torch.nn as nn
+
+        for g in self.groups:
+            for p in g.bcast_params:
+                p._fused_linear = False
+                if p.is_owner or len(p.alias_sites) != 1 or len(p._orig_size) != 2 or p._param_dtype != torch.bfloat16:
+                    continue
+                mod, attr = p.alias_sites[0]
+                if type(mod) is not nn.Linear or attr != "weight" or p._orig_size[1] % 32 != 0:
+                    continue
+                p._fused_linear = True
+                p._fused_epoch = -1
+                mod._dmuon_fused = (self, p)
+                mod.forward = types.MethodType(_fused_linear_forward, mod)
+
+    def fused_pull_args(self, p: DedicatedParam):
+        esz = self.pub.element_size()
+        remote = self.pub_ptrs[p.owner_shard] + p._arena_offset * esz
+        flag = self.flags[KIND_PUB_READY * MAX_PEERS + p.owner_shard :]
+        from ..ops import peer as P
+
+        return remote, flag, self.pub_epoch, P.wait_budget_cycles()
 
     # ------------------------------------------------------------------ helpers
     def _signal(self, kind: int, value: int) -> None:
@@ -198,27 +257,39 @@ class PeerRuntime:
 
         if g._pulled_epoch == self.pub_epoch:
             return
-        srcs, dsts, nbytes, slots = [], [], [], []
-        esz = self.pub.element_size()
-        for s, plist in g._pub_by_shard.items():
-            if s == self.rank:
-                continue
-            # the parameters of one owner inside one group are adjacent: one copy per owner
-            lo = min(p._arena_offset for p in plist)
-            hi = max(p._arena_offset + (p.numel + ALIGN - 1) // ALIGN * ALIGN for p in plist)
-            srcs.append(self.pub_ptrs[s] + lo * esz)
-            dsts.append(self.pub.data_ptr() + lo * esz)
-            nbytes.append((hi - lo) * esz)
-            slots.append(KIND_PUB_READY * MAX_PEERS + s)
-        if srcs:
-            live = tuple(p._unsharded_param for p in g.bcast_params)
-            with torch.no_grad(), torch.autograd._unsafe_preserve_version_counter(live):
-                P.peer_pull(srcs, dsts, nbytes, slots, self.flags, self.pub_epoch, self.status, self.device,
-                            blocks_per_tensor=max(4, 32 // len(srcs)))
+        remote = [p for s, plist in g._pub_by_shard.items() if s != self.rank for p in plist]
+        if remote:
+            # weights consumed by a fused linear are fetched by that kernel instead
+            self.pull_params([p for p in remote if not getattr(p, "_fused_linear", False)])
             self._pulled_groups += 1
-            if self._pulled_groups == self._remote_groups:
+            if self._pulled_groups == self._remote_groups and not self.fused_forward:
                 self._signal(KIND_PUB_CONSUMED, self.pub_epoch)
         g._pulled_epoch = self.pub_epoch
+
+    def pull_params(self, plist: list[DedicatedParam]) -> None:
+        """Copy the listed slots from their owners (current stream); adjacent
+        slots of one owner travel as one span."""
+        from ..ops import peer as P
+
+        if not plist:
+            return
+        esz = self.pub.element_size()
+        spans: list[list[int]] = []            # [owner, lo, hi] in elements
+        for p in sorted(plist, key=lambda q: q._arena_offset):
+            lo = p._arena_offset
+            hi = lo + (p.numel + ALIGN - 1) // ALIGN * ALIGN
+            if spans and spans[-1][0] == p.owner_shard and spans[-1][2] == lo:
+                spans[-1][2] = hi
+            else:
+                spans.append([p.owner_shard, lo, hi])
+        srcs = [self.pub_ptrs[s] + lo * esz for s, lo, _ in spans]
+        dsts = [self.pub.data_ptr() + lo * esz for _, lo, _ in spans]
+        nbytes = [(hi - lo) * esz for _, lo, hi in spans]
+        slots = [KIND_PUB_READY * MAX_PEERS + s for s, _, _ in spans]
+        live = tuple(p._unsharded_param for p in plist)
+        with torch.no_grad(), torch.autograd._unsafe_preserve_version_counter(live):
+            P.peer_pull(srcs, dsts, nbytes, slots, self.flags, self.pub_epoch, self.status, self.device,
+                        blocks_per_tensor=max(4, 32 // len(srcs)))
 
     # ------------------------------------------------------------------ gradient side
     def before_pack(self) -> None:
@@ -233,6 +304,10 @@ class PeerRuntime:
         if not self._grads_signalled:
             self._signal(KIND_GRAD_READY, self.grad_epoch + 1)
             self._grads_signalled = True
+            if self.fused_forward and self._remote_groups > 0:
+                # fused linears pull on the compute stream during forward; this point
+                # is stream-ordered after all of them
+                self._signal(KIND_PUB_CONSUMED, self.pub_epoch)
 
     def source_for(self, dparams: list[DedicatedParam]) -> PeerSource:
         return PeerSource(self, dparams)

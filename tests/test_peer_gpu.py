@@ -66,6 +66,43 @@ def test_pull_and_signal_on_one_device():
     assert torch.equal(src, dst)
 
 
+@pytest.mark.parametrize("M,N,K", [(1000, 600, 512), (4096, 1024, 2048), (300, 256, 96), (128, 2304, 1152)])
+def test_pull_linear_fetches_and_multiplies(M, N, K):
+    """The "owner" is a second buffer on the same GPU: the kernel must leave an
+    exact copy in the local slot and multiply with it."""
+    import torch.nn.functional as F
+
+    from dmuon_b200.ops import gemm as G
+    from dmuon_b200.ops import pull_linear as PL
+
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(3)
+    x = (torch.randn(M, K, device=dev) * 0.1).bfloat16()
+    w_owner = (torch.randn(N, K, device=dev) * 0.1).bfloat16()
+    w_local = torch.zeros_like(w_owner)
+    flag = torch.full((4,), 3, dtype=torch.int32, device=dev)
+    y = PL.pull_linear(x, w_local, w_owner.data_ptr(), pub_flag=flag[1:], pub_want=3)
+    torch.cuda.synchronize()
+    G.check_status(dev)
+    assert torch.equal(w_local, w_owner)
+    ref = F.linear(x.float(), w_owner.float())
+    assert (y.float() - ref).abs().max().item() < 2e-2 * (ref.abs().max().item() + 1e-6)
+    # second use in the same epoch: plain multiplication with the local copy
+    y2 = PL.pull_linear(x, w_local)
+    torch.cuda.synchronize()
+    assert torch.equal(y, y2)
+    # autograd wrapper
+    xg = x.clone().requires_grad_(True)
+    wp = torch.nn.Parameter(torch.zeros_like(w_owner))
+    out = PL.PulledLinearFn.apply(xg, wp, None, w_owner.data_ptr(), flag[1:], 3, 0)
+    out.float().square().sum().backward()
+    xr = x.float().clone().requires_grad_(True)
+    wr = w_owner.float().clone().requires_grad_(True)
+    F.linear(xr, wr).bfloat16().float().square().sum().backward()
+    assert (xg.grad.float() - xr.grad).abs().max().item() < 3e-2 * (xr.grad.abs().max().item() + 1e-6)
+    assert (wp.grad.float() - wr.grad).abs().max().item() < 3e-2 * (wr.grad.abs().max().item() + 1e-6)
+
+
 def test_flag_wait_times_out_cleanly():
     """A flag nobody sets: the wait gives up after its budget, reports status 4
     and the context stays usable."""
@@ -94,6 +131,11 @@ def _train_body(rank, world, backend, steps):
     import dmuon_b200 as dmuon
     from dmuon_b200.models.llama import LlamaConfig, LlamaModel
 
+    import os
+
+    if backend == "peer-fused":
+        os.environ["DMUON_FUSED_PUBLISH"] = "1"
+        backend = "peer"
     dev = torch.device("cuda", rank)
     cfg = LlamaConfig(vocab_size=2048, d_model=512, n_layers=3, n_heads=8, n_kv_heads=4, head_dim=64,
                       ffn_hidden=1536, rope_theta=10000.0)
@@ -153,8 +195,27 @@ def test_peer_data_plane_matches_nccl():
         assert rel < 0.15, (k, rel)
 
 
-def _reduce_check_body(rank, world):
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_forward_publish_matches_nccl():
+    """Weights pulled inside the first forward GEMM instead of by a copy kernel."""
+    steps = 4
+    ref = run_ranks(_train_body, 2, args=("nccl", steps), backend="nccl", timeout=600)
+    got = run_ranks(_train_body, 2, args=("peer-fused", steps), backend="nccl", timeout=600)
+    assert got[0][2]
+    for a, b in zip(got[0][0], ref[0][0]):
+        assert abs(a - b) < 2e-2 * max(1.0, abs(b)), (got[0][0], ref[0][0])
+    for k, v in ref[0][1].items():
+        rel = (got[0][1][k].float() - v.float()).norm().item() / (v.float().norm().item() + 1e-12)
+        assert rel < 0.15, (k, rel)
+
+
+def _reduce_check_body(rank, world, fused=False):
+    import os
+
     import torch.distributed as dist
+
+    if fused:
+        os.environ["DMUON_FUSED_PUBLISH"] = "1"
     from torch.distributed.device_mesh import init_device_mesh
     from torch.distributed.fsdp import fully_shard
 
@@ -203,7 +264,8 @@ def _reduce_check_body(rank, world):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_peer_reduce_and_publish_are_exact():
+@pytest.mark.parametrize("fused", [False, True])
+def test_peer_reduce_and_publish_are_exact(fused):
     world = min(4, torch.cuda.device_count())
-    worst = run_ranks(_reduce_check_body, world, backend="nccl", timeout=600)
+    worst = run_ranks(_reduce_check_body, world, args=(fused,), backend="nccl", timeout=600)
     assert max(worst) < 1e-5, worst

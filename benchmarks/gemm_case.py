@@ -29,6 +29,7 @@ def main():
     ap.add_argument("--with-c", action="store_true")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--two-cta", action="store_true", help="CTA-pair kernel (cta_group::2, 256 x 256 tiles)")
     ap.add_argument("--cublas", action="store_true", help="also time torch.bmm on the same operands")
     args = ap.parse_args()
     import torch
@@ -52,7 +53,7 @@ def main():
 
     def run():
         G.gemm(A, B, out, a_mn=args.a_mn, b_mn=b_mn, C=C, beta=0.5 if C is not None else 0.0,
-               symmetric=args.symmetric, bn=args.bn)
+               symmetric=args.symmetric, bn=args.bn, two_cta=args.two_cta)
 
     for _ in range(args.warmup):
         run()
@@ -69,7 +70,7 @@ def main():
     G.check_status(dev)
     ms = sorted(times)[len(times) // 2]
     rec = {"M": M, "N": N, "K": K, "batch": L, "bn": args.bn, "a_mn": args.a_mn, "b_mn": b_mn,
-           "symmetric": args.symmetric, "ms": round(ms, 4), "dense_tflops": round(2.0 * M * N * K * L / ms / 1e9, 1)}
+           "symmetric": args.symmetric, "two_cta": args.two_cta, "ms": round(ms, 4), "dense_tflops": round(2.0 * M * N * K * L / ms / 1e9, 1)}
     if args.cublas:
         Af = A.transpose(1, 2) if args.a_mn else A
         Bf = B if b_mn else B.transpose(1, 2)

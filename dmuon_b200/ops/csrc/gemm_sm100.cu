@@ -394,6 +394,238 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 }
 
+// ---- CTA-pair kernel (tcgen05 cta_group::2) -------------------------------------
+//
+// Two CTAs of a cluster share one 256 x 256 output tile.  Each CTA stages its
+// own 128 rows of A and its own 128 of the 256 B columns, the leader (even
+// rank) issues 256 x 256 x 16 MMAs that read both CTAs' shared memory, and each
+// CTA ends up with its 128 rows of the accumulator in its own TMEM.  Per
+// k-block a CTA now pulls 32 KB from L2 for the work that took 48 KB with the
+// single-CTA kernel -- the L2 feed is what limits that kernel (ncu: tensor pipe
+// 75 % busy, 16 TB/s from L2).  No multicast: every load is issued by the CTA
+// that consumes it; only barrier signals cross the pair.
+constexpr int kPairStages = 6;
+constexpr int kPairABytes = BM * BK * 2;            // 128 rows per CTA
+constexpr int kPairBBytes = 128 * BK * 2;           // 128 of the 256 columns per CTA
+constexpr int kPairStageBytes = kPairABytes + kPairBBytes;
+constexpr int kPairBN = 256;
+constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 256 + 1024;
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const KParams p) {
+  constexpr int S = kPairStages;
+  constexpr int BNp = kPairBN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + S * kPairABytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * kPairStageBytes);
+  const uint32_t full0 = smem_u32(bars);
+  const uint32_t empty0 = smem_u32(bars + S);
+  const uint32_t tfull0 = smem_u32(bars + 2 * S);
+  const uint32_t tempty0 = smem_u32(bars + 2 * S + 2);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();          // 0 = leader
+  const bool leader = rank == 0;
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(full0 + 8 * s, 1);      // used on the leader: its own arrive + both CTAs' bytes
+      mbar_init(empty0 + 8 * s, 1);     // one commit from the leader's MMA thread, in each CTA
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull0 + 8 * a, 1);     // one commit from the leader, in each CTA
+      mbar_init(tempty0 + 8 * a, 8);    // used on the leader: 4 epilogue warps of each CTA
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), 2 * BNp);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();                    // both CTAs' barriers exist before anything crosses the pair
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_tiles = p.tiles_per_batch * p.batch;
+  const int num_kb = (p.K + BK - 1) / BK;
+  int fail_code = 0;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- TMA producer (both CTAs) ----------------
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = pair_id; ok && t < total_tiles; t += num_pairs) {
+        const int b = t / p.tiles_per_batch;
+        const int4 e = p.tile_tab[t - b * p.tiles_per_batch];
+        const int m0 = e.x * 256 + 128 * static_cast<int>(rank);
+        const int n0 = e.y * BNp + 128 * static_cast<int>(rank);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(empty0 + 8 * stage, phase ^ 1u, abort_flag)) {
+            ok = false;
+            fail_code = kStatusTimeoutProducer;
+            break;
+          }
+          if (leader) mbar_arrive_expect_tx(full0 + 8 * stage, 2 * kPairStageBytes);
+          const uint32_t fb = (full0 + 8 * stage) & 0xFEFFFFFFu;     // the leader's barrier
+          const uint32_t a_dst = smem_u32(sA + stage * kPairABytes);
+          const uint32_t b_dst = smem_u32(sB + stage * kPairBBytes);
+          if (!p.a_mn_major) {
+            tma_load_3d_pair(a_dst, &tmA, fb, kb * BK, m0, b);
+          } else {
+#pragma unroll
+            for (int mb = 0; mb < 2; ++mb)
+              tma_load_3d_pair(a_dst + mb * kBlockBytes, &tmA, fb, m0 + 64 * mb, kb * BK, b);
+          }
+          if (!p.b_mn_major) {
+            tma_load_3d_pair(b_dst, &tmB, fb, kb * BK, n0, b);
+          } else {
+#pragma unroll
+            for (int nb = 0; nb < 2; ++nb)
+              tma_load_3d_pair(b_dst + nb * kBlockBytes, &tmB, fb, n0 + 64 * nb, kb * BK, b);
+          }
+          if (++stage == S) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      // ---------------- MMA issuer (leader only) ----------------
+      const uint32_t idesc =
+          make_idesc_f16(256, BNp, p.ab_fp16 != 0, p.a_mn_major != 0, p.b_mn_major != 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = pair_id; ok && t < total_tiles; t += num_pairs) {
+        if (!mbar_wait_bounded(tempty0 + 8 * acc, acc_phase ^ 1u, abort_flag)) {
+          fail_code = kStatusTimeoutMma;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BNp);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(full0 + 8 * stage, phase, abort_flag)) {
+            ok = false;
+            fail_code = kStatusTimeoutMma;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_base = smem_u32(sA + stage * kPairABytes);
+          const uint32_t b_base = smem_u32(sB + stage * kPairBBytes);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adesc = p.a_mn_major
+                                       ? make_smem_desc_sw128(a_base + k * 2048, kBlockBytes, 1024)
+                                       : make_smem_desc_sw128(a_base + k * 32, 16, 1024);
+            const uint64_t bdesc = p.b_mn_major
+                                       ? make_smem_desc_sw128(b_base + k * 2048, kBlockBytes, 1024)
+                                       : make_smem_desc_sw128(b_base + k * 32, 16, 1024);
+            umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          // free the stage in both CTAs
+          umma_commit_pair(mapa_shared(empty0 + 8 * stage, 0));
+          umma_commit_pair(mapa_shared(empty0 + 8 * stage, 1));
+          if (++stage == S) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit_pair(mapa_shared(tfull0 + 8 * acc, 0));
+        umma_commit_pair(mapa_shared(tfull0 + 8 * acc, 1));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5 of both CTAs) ----------------
+    const int q = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = pair_id; t < total_tiles; t += num_pairs) {
+      const int b = t / p.tiles_per_batch;
+      const int4 e = p.tile_tab[t - b * p.tiles_per_batch];
+      const int m0 = e.x * 256 + 128 * static_cast<int>(rank);
+      const int n0 = e.y * BNp;
+      const bool mirror = (e.z & 1) != 0;
+      if (!mbar_wait_bounded(tfull0 + 8 * acc, acc_phase, abort_flag)) {
+        fail_code = kStatusTimeoutEpilogue;
+        break;
+      }
+      tc_fence_after_sync();
+      const int row = m0 + q * 32 + lane;
+      const char* Cb = reinterpret_cast<const char*>(p.C_tab ? p.C_tab[b] : p.C);
+      char* Db = reinterpret_cast<char*>(p.D_tab ? p.D_tab[b] : p.D);
+      __nv_bfloat16* D2b = reinterpret_cast<__nv_bfloat16*>(p.D2_tab ? p.D2_tab[b] : p.D2);
+      const int esz = (p.out_kind == 2) ? 4 : 2;
+      if (!p.C_tab && Cb) Cb += static_cast<long long>(b) * p.strideC * esz;
+      if (!p.D_tab) Db += static_cast<long long>(b) * p.strideD * esz;
+      if (!p.D2_tab && D2b) D2b += static_cast<long long>(b) * p.strideD2;
+      const float alpha = p.alpha_vec ? p.alpha * p.alpha_vec[b] : p.alpha;
+      for (int c = 0; c < BNp; c += 32) {
+        const int col0 = n0 + c;
+        if (col0 >= p.N) break;
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BNp + c), r);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = alpha * __uint_as_float(r[j]);
+        if (p.out_kind == 0) {
+          epilogue_chunk<__nv_bfloat16>(p, reinterpret_cast<const __nv_bfloat16*>(Cb),
+                                        reinterpret_cast<__nv_bfloat16*>(Db), D2b, v, row, col0, mirror);
+        } else if (p.out_kind == 1) {
+          epilogue_chunk<__half>(p, reinterpret_cast<const __half*>(Cb), reinterpret_cast<__half*>(Db), D2b, v,
+                                 row, col0, mirror);
+        } else {
+          epilogue_chunk<float>(p, reinterpret_cast<const float*>(Cb), reinterpret_cast<float*>(Db), D2b, v, row,
+                                col0, mirror);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(tempty0 + 8 * acc, 0));   // the leader's barrier
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    if (fail_code != 0 && p.status != nullptr) atomicCAS(p.status, 0, fail_code);
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    __syncthreads();
+  }
+  cluster_sync_all();                    // the peer may still read this CTA's shared memory until here
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, 2 * BNp);
+  }
+}
+
 // ---- host side ------------------------------------------------------------------
 
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -472,6 +704,54 @@ static int launch(const DmuonGemmArgs& a, const CUtensorMap& tmA, const CUtensor
   return static_cast<int>(cudaGetLastError());
 }
 
+static int launch_pair(const DmuonGemmArgs& a, const CUtensorMap& tmA, const CUtensorMap& tmB,
+                       cudaStream_t stream, int num_sms) {
+  static bool attr_set[16] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 16 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kPairSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set[dev] = true;
+  }
+  KParams p;
+  p.M = a.M; p.N = a.N; p.K = a.K; p.batch = a.batch;
+  p.tile_tab = reinterpret_cast<const int4*>(a.tile_tab);
+  p.tiles_per_batch = a.tiles_per_batch;
+  p.a_mn_major = a.a_mn_major; p.b_mn_major = a.b_mn_major; p.ab_fp16 = a.ab_fp16;
+  p.alpha = a.alpha; p.beta = a.beta; p.diag = a.diag;
+  p.alpha_vec = a.alpha_vec;
+  p.C = a.C; p.D = a.D; p.D2 = a.D2;
+  p.C_tab = a.C_tab; p.D_tab = a.D_tab; p.D2_tab = a.D2_tab;
+  p.ldc = a.ldc; p.ldd = a.ldd; p.ldd2 = a.ldd2;
+  p.strideC = a.strideC; p.strideD = a.strideD; p.strideD2 = a.strideD2;
+  p.out_kind = a.out_kind;
+  p.b_ready = nullptr; p.b_ready_epoch = 0;
+  p.status = a.status;
+  if (p.C == nullptr && p.C_tab == nullptr) p.beta = 0.f;
+  const long long total = static_cast<long long>(a.tiles_per_batch) * a.batch;
+  int pairs = num_sms / 2;
+  if (a.max_ctas > 0 && a.max_ctas / 2 < pairs) pairs = a.max_ctas / 2;
+  if (total < pairs) pairs = static_cast<int>(total);
+  if (pairs <= 0) return 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = kPairSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel, tmA, tmB, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
+}
+
 }  // namespace dmuon
 
 extern "C" long long dmuon_launch_count(void) {
@@ -504,6 +784,16 @@ extern "C" int dmuon_gemm_sm100(const DmuonGemmArgs* args, void* stream_v) {
   else
     rc = make_map(&tmA, a.A, a.ab_fp16 != 0, a.M, a.K, a.batch, a.lda, a.strideA, 64, BK);
   if (rc != 0) return rc;
+  if (a.two_cta) {
+    if (a.bn != 256) return -1;
+    // each CTA of a pair loads 128 of the 256 B columns
+    if (!a.b_mn_major)
+      rc = make_map(&tmB, a.B, a.ab_fp16 != 0, a.K, a.N, a.batch, a.ldb, a.strideB, BK, 128);
+    else
+      rc = make_map(&tmB, a.B, a.ab_fp16 != 0, a.N, a.K, a.batch, a.ldb, a.strideB, 64, BK);
+    if (rc != 0) return rc;
+    return launch_pair(a, tmA, tmB, stream, sms);
+  }
   if (!a.b_mn_major)
     rc = make_map(&tmB, a.B, a.ab_fp16 != 0, a.K, a.N, a.batch, a.ldb, a.strideB, BK, a.bn);
   else

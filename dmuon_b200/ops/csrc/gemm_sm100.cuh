@@ -49,6 +49,9 @@ struct DmuonGemmArgs {
 
   int* status;                 // device int; set non-zero when a wait ran out
   int max_ctas;                // 0 = one CTA per SM
+  // 1: run on CTA pairs (tcgen05 cta_group::2).  The tile list is then in units
+  // of 256 rows x 256 columns and bn must be 256.
+  int two_cta;
 };
 
 // Returns 0 on success, a cudaError_t / negative code otherwise.

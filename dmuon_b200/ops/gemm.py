@@ -64,6 +64,7 @@ class _GemmArgs(ctypes.Structure):
         ("b_ready_epoch", ctypes.c_int),
         ("status", ctypes.c_void_p),
         ("max_ctas", ctypes.c_int),
+        ("two_cta", ctypes.c_int),
     ]
 
 
@@ -96,7 +97,7 @@ def check_status(device: torch.device | None = None) -> None:
         raise KernelTimeout(f"dmuon_b200 kernel wait ran out (code {code}: {names.get(code, '?')})")
 
 
-def symmetric_tiles(m: int, bn: int) -> list[tuple[int, int, int]]:
+def symmetric_tiles(m: int, bn: int, bm: int = BM) -> list[tuple[int, int, int]]:
     """Tiles (row_tile, col_tile, mirror) covering the lower triangle of m x m.
 
     A tile is kept when any of its elements has row >= col; a tile whose
@@ -104,27 +105,29 @@ def symmetric_tiles(m: int, bn: int) -> list[tuple[int, int, int]]:
     transposed.  Tiles that straddle the diagonal store what they compute.
     """
     out = []
-    mt = (m + BM - 1) // BM
+    mt = (m + bm - 1) // bm
     for i in range(mt):
-        last_row = min(m, (i + 1) * BM) - 1
+        last_row = min(m, (i + 1) * bm) - 1
         for j in range(last_row // bn + 1):
-            mirror = 1 if (j + 1) * bn <= i * BM else 0
+            mirror = 1 if (j + 1) * bn <= i * bm else 0
             out.append((i, j, mirror))
     return out
 
 
-def dense_tiles(m: int, n: int, bn: int) -> list[tuple[int, int, int]]:
-    mt = (m + BM - 1) // BM
+def dense_tiles(m: int, n: int, bn: int, bm: int = BM) -> list[tuple[int, int, int]]:
+    mt = (m + bm - 1) // bm
     nt = (n + bn - 1) // bn
     # column tile outermost: CTAs that run at the same time share B tiles in L2
     return [(i, j, 0) for j in range(nt) for i in range(mt)]
 
 
-def tile_table(m: int, n: int, bn: int, symmetric: bool, device: torch.device) -> tuple[torch.Tensor, int]:
-    key = (m, n, bn, symmetric, device.index)
+def tile_table(m: int, n: int, bn: int, symmetric: bool, device: torch.device, bm: int = BM) -> tuple[torch.Tensor, int]:
+    """Device table of (row_tile, col_tile, flags, 0); row tiles are ``bm`` rows
+    (128 for the single-CTA kernel, 256 for CTA pairs)."""
+    key = (m, n, bn, symmetric, device.index, bm)
     hit = _tile_cache.get(key)
     if hit is None:
-        tiles = symmetric_tiles(m, bn) if symmetric else dense_tiles(m, n, bn)
+        tiles = symmetric_tiles(m, bn, bm) if symmetric else dense_tiles(m, n, bn, bm)
         flat = [[i, j, f, 0] for (i, j, f) in tiles]
         tab = torch.tensor(flat, dtype=torch.int32).to(device)
         hit = (tab, len(tiles))
@@ -139,6 +142,18 @@ def _fn():
     fn.argtypes = [ctypes.POINTER(_GemmArgs), ctypes.c_void_p]
     fn.restype = ctypes.c_int
     return fn
+
+
+#: run large products on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles)
+TWO_CTA_DEFAULT = True
+
+
+def pair_kernel_pays(m: int, n: int, batch: int, symmetric: bool) -> bool:
+    """CTA pairs need enough 256 x 256 tiles to keep 74 pairs busy."""
+    if m < 256 or n < 256:
+        return False
+    tiles = len(symmetric_tiles(m, 256, 256)) if symmetric else ((m + 255) // 256) * ((n + 255) // 256)
+    return tiles * batch >= 74
 
 
 def pick_bn(m: int, n: int, batch: int, symmetric: bool) -> int:
@@ -173,6 +188,7 @@ def gemm(
     b_ready: torch.Tensor | None = None,
     b_ready_epoch: int = 0,
     max_ctas: int = 0,
+    two_cta: bool | None = None,
 ) -> torch.Tensor:
     """Launch one batched product on the current CUDA stream.
 
@@ -204,7 +220,11 @@ def gemm(
     dev = A.device
     if bn is None:
         bn = pick_bn(M, N, batch, symmetric)
-    tab, ntiles = tile_table(M, N, bn, symmetric, dev)
+    if two_cta is None:
+        two_cta = TWO_CTA_DEFAULT and pair_kernel_pays(M, N, batch, symmetric)
+    if two_cta:
+        bn = 256
+    tab, ntiles = tile_table(M, N, bn, symmetric, dev, 256 if two_cta else BM)
 
     args = _GemmArgs()
     args.A = A.data_ptr()
@@ -264,6 +284,7 @@ def gemm(
         args.b_ready_epoch = int(b_ready_epoch)
     args.status = status_buffer(dev).data_ptr()
     args.max_ctas = int(max_ctas)
+    args.two_cta = int(bool(two_cta))
     rc = _fn()(ctypes.byref(args), ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
     if rc != 0:
         raise RuntimeError(f"dmuon_gemm_sm100 failed with code {rc}")

@@ -37,6 +37,9 @@ from .dparam import DedicatedParam
 KIND_GRAD_READY, KIND_GRAD_CONSUMED, KIND_PUB_READY, KIND_PUB_CONSUMED = 0, 1, 2, 3
 MAX_PEERS = 8
 ALIGN = 64          # elements; keeps every slot 128-byte aligned for bf16
+#: CTAs per tensor of the in-backward reduce: enough loads in flight for NVLink
+#: (about 28 KB per CTA) without taking many SMs from the backward GEMMs
+REDUCE_BLOCKS_PER_TENSOR = 24
 
 
 def peer_backend_requested() -> str:
@@ -130,7 +133,13 @@ class PeerRuntime:
         self.total = max(off, ALIGN)
         self.pub = symm_mem.empty(self.total, dtype=self.param_dtype, device=self.device)
         self.grad = symm_mem.empty(self.total, dtype=self.grad_dtype, device=self.device)
-        self.flags = symm_mem.empty(4 * MAX_PEERS, dtype=torch.int32, device=self.device)
+        # four global epoch rows, then one "gradients packed" row per group
+        self.flags = symm_mem.empty((4 + len(groups)) * MAX_PEERS, dtype=torch.int32, device=self.device)
+        self.reduce_mode = os.environ.get("DMUON_PEER_REDUCE", "backward").strip().lower()
+        if self.reduce_mode not in ("backward", "optimizer"):
+            raise ValueError("DMUON_PEER_REDUCE must be 'backward' or 'optimizer'")
+        for i, g in enumerate(groups):
+            g._group_index = i
         self.flags.zero_()
         self.grad.zero_()
         torch.cuda.synchronize(self.device)
@@ -309,6 +318,31 @@ class PeerRuntime:
                 # is stream-ordered after all of them
                 self._signal(KIND_PUB_CONSUMED, self.pub_epoch)
 
+    # per-group reduce that overlaps with the rest of backward ("backward" mode)
+    def signal_group_packed(self, g: "PeerParamGroup", count: int) -> None:
+        from ..ops import peer as P
+
+        P.signal_peers(self.flag_ptrs, (4 + g._group_index) * MAX_PEERS + self.rank, count, self.device)
+
+    def launch_group_reduce(self, g: "PeerParamGroup", owned: list[DedicatedParam], count: int):
+        """Queue, on the reduce lane, the kernel that sums this group's owned
+        gradients over all ranks' arenas as soon as every rank has packed them."""
+        from ..ops import peer as P
+
+        lane = self.ctx.reduce_lane
+        for p in owned:
+            if getattr(p, "_reduce_buf", None) is None:
+                p._reduce_buf = torch.empty(p._orig_size, dtype=torch.float32, device=self.device)
+        lane.follow_current()
+        src = self.source_for(owned)
+        base = (4 + g._group_index) * MAX_PEERS
+        with lane.use():
+            P.peer_prologue(src.peer_bases, src.offsets, src.numels, src.grad_dtype, [None] * len(owned),
+                            [p._reduce_buf.reshape(-1) for p in owned], [0] * len(owned), None, scale=src.scale,
+                            mu=0.0, nesterov=False, ready_flags=self.flags[base:], ready_want=count,
+                            status=self.status, max_blocks_per_tensor=REDUCE_BLOCKS_PER_TENSOR)
+        return lane.mark()
+
     def source_for(self, dparams: list[DedicatedParam]) -> PeerSource:
         return PeerSource(self, dparams)
 
@@ -352,6 +386,9 @@ class PeerParamGroup(DedicatedParamGroup):
         self.runtime: Optional[PeerRuntime] = None
         self._pulled_epoch = -1
         self._packed_this_step = False
+        self._pack_count = 0
+        self._reduce_ticket = None
+        self._reduce_owned: list = []
         super().__init__(*args, **kwargs)
 
     def _build_packed_buffers(self) -> None:
@@ -407,11 +444,35 @@ class PeerParamGroup(DedicatedParamGroup):
                 p._peer_grad_pending = True
                 p.clear_local_grad()
         self._packed_this_step = True
+        if rt.reduce_mode == "backward" and not self._no_sync:
+            # tell every rank this group's running sum is in the arena, then (as an
+            # owner) reduce it on the side lane while backward continues.  A later
+            # micro-batch repeats this and overwrites the result with the larger sum.
+            self._pack_count += 1
+            rt.signal_group_packed(self, self._pack_count)
+            owned = [p for p, _ in with_grad if p.is_owner]
+            if owned:
+                self._reduce_ticket = rt.launch_group_reduce(self, owned, self._pack_count)
+                self._reduce_owned = owned
 
     def has_pending_reduce(self) -> bool:
+        if self._reduce_ticket is not None:
+            return True
         return self._packed_this_step and not self.runtime._grads_signalled
 
+    def wait_for_stage1_reduce(self) -> None:
+        return      # reduce kernels only read; nothing to throttle
+
     def wait_for_reduce(self, lane=None) -> None:
-        # nothing travels until the owner's prologue reads the arenas; make sure
-        # the "gradients ready" epoch is announced after the last pack
+        if self._reduce_ticket is not None:
+            if lane is not None:
+                self._reduce_ticket.wait_on(lane)
+            else:
+                self._reduce_ticket.wait_on_current()
+            self._reduce_ticket = None
+            for p in self._reduce_owned:
+                p._reduced_grad = p._reduce_buf
+            self._reduce_owned = []
+        # "optimizer" mode: nothing travels until the owner's prologue reads the
+        # arenas; the "gradients ready" epoch is announced after the last pack
         self.runtime.announce_grads()

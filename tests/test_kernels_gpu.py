@@ -74,6 +74,55 @@ def test_gemm_matches_fp32(case):
         assert (out2.float() - ref).abs().max().item() / scale < 2e-2
 
 
+PAIR_CASES = [
+    # M, N, K, batch, a_mn, b_mn, symmetric, out dtype, epilogue
+    (256, 256, 64, 1, False, False, False, torch.bfloat16, False),
+    (512, 768, 1024, 2, False, False, False, torch.bfloat16, True),
+    (384, 640, 320, 1, False, False, False, torch.bfloat16, False),      # ragged in M and N
+    (512, 1024, 512, 1, False, True, False, torch.float32, True),
+    (512, 512, 512, 1, True, False, False, torch.bfloat16, False),
+    (768, 512, 448, 1, True, True, False, torch.bfloat16, False),
+    (1024, 1024, 512, 3, False, False, True, torch.bfloat16, True),
+    (1152, 1152, 4304, 1, False, False, True, torch.bfloat16, False),
+    (512, 512, 1024, 2, True, True, True, torch.float16, True),
+]
+
+
+@pytest.mark.parametrize("case", PAIR_CASES, ids=[f"pair{i}" for i in range(len(PAIR_CASES))])
+def test_gemm_pair_kernel_matches_fp32(case):
+    """CTA-pair kernel (tcgen05 cta_group::2, 256 x 256 tiles)."""
+    from dmuon_b200.ops import gemm as G
+
+    M, N, K, batch, a_mn, b_mn, sym, odt, epi = case
+    dt = torch.float16 if odt == torch.float16 else torch.bfloat16
+    dev = _dev()
+    torch.manual_seed(0)
+    if sym:
+        X = (torch.randn(batch, M, K, device=dev) * 0.1).to(dt)
+        A = X.transpose(1, 2).contiguous() if a_mn else X
+        B = X.transpose(1, 2).contiguous() if b_mn else X
+    else:
+        A = ((torch.randn(batch, K, M, device=dev) if a_mn else torch.randn(batch, M, K, device=dev)) * 0.1).to(dt)
+        B = ((torch.randn(batch, K, N, device=dev) if b_mn else torch.randn(batch, N, K, device=dev)) * 0.1).to(dt)
+    C = None
+    alpha, beta, diag = 1.0, 0.0, 0.0
+    if epi:
+        C = torch.randn(batch, M, N, device=dev)
+        if sym:
+            C = C + C.transpose(1, 2)
+        C = C.to(odt)
+        alpha, beta, diag = 1.5, -0.5, (0.3 if M == N else 0.0)
+    out = torch.full((batch, M, N), float("nan"), device=dev, dtype=odt)
+    G.gemm(A, B, out, a_mn=a_mn, b_mn=b_mn, C=C, alpha=alpha, beta=beta, diag=diag, symmetric=sym, two_cta=True)
+    torch.cuda.synchronize()
+    G.check_status(dev)
+    ref = _ref_gemm(A, B, a_mn, b_mn, C, alpha, beta, diag)
+    scale = ref.abs().max().item() + 1e-6
+    tol = 2e-2 if odt != torch.float32 else 2e-3
+    assert not torch.isnan(out.float()).any()
+    assert (out.float() - ref).abs().max().item() / scale < tol
+
+
 def test_gemm_alpha_vec_and_pointer_tables():
     from dmuon_b200.ops import gemm as G
 

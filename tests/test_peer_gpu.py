@@ -136,6 +136,9 @@ def _train_body(rank, world, backend, steps):
     if backend == "peer-fused":
         os.environ["DMUON_FUSED_PUBLISH"] = "1"
         backend = "peer"
+    if backend == "peer-optimizer-reduce":
+        os.environ["DMUON_PEER_REDUCE"] = "optimizer"
+        backend = "peer"
     dev = torch.device("cuda", rank)
     cfg = LlamaConfig(vocab_size=2048, d_model=512, n_layers=3, n_heads=8, n_kv_heads=4, head_dim=64,
                       ffn_hidden=1536, rope_theta=10000.0)
@@ -183,9 +186,11 @@ def test_peer_data_plane_matches_nccl():
     steps = 4
     ref = run_ranks(_train_body, world, args=("nccl", steps), backend="nccl", timeout=600)
     got = run_ranks(_train_body, world, args=("peer", steps), backend="nccl", timeout=600)
-    assert not ref[0][2] and got[0][2]
-    for a, b in zip(got[0][0], ref[0][0]):
+    alt = run_ranks(_train_body, world, args=("peer-optimizer-reduce", steps), backend="nccl", timeout=600)
+    assert not ref[0][2] and got[0][2] and alt[0][2]
+    for a, b, c in zip(got[0][0], ref[0][0], alt[0][0]):
         assert abs(a - b) < 2e-2 * max(1.0, abs(b)), (got[0][0], ref[0][0])
+        assert abs(c - b) < 2e-2 * max(1.0, abs(b)), (alt[0][0], ref[0][0])
     # Two separate runs never see bit-identical gradients (the attention backward
     # and the sharded reductions are not deterministic) and Newton-Schulz amplifies
     # such differences along weak singular directions, so this end-to-end check is a
@@ -209,11 +214,12 @@ def test_fused_forward_publish_matches_nccl():
         assert rel < 0.15, (k, rel)
 
 
-def _reduce_check_body(rank, world, fused=False):
+def _reduce_check_body(rank, world, fused=False, reduce_mode="backward"):
     import os
 
     import torch.distributed as dist
 
+    os.environ["DMUON_PEER_REDUCE"] = reduce_mode
     if fused:
         os.environ["DMUON_FUSED_PUBLISH"] = "1"
     from torch.distributed.device_mesh import init_device_mesh
@@ -264,8 +270,8 @@ def _reduce_check_body(rank, world, fused=False):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("fused", [False, True])
-def test_peer_reduce_and_publish_are_exact(fused):
+@pytest.mark.parametrize("fused,reduce_mode", [(False, "backward"), (True, "backward"), (False, "optimizer")])
+def test_peer_reduce_and_publish_are_exact(fused, reduce_mode):
     world = min(4, torch.cuda.device_count())
-    worst = run_ranks(_reduce_check_body, world, args=(fused,), backend="nccl", timeout=600)
+    worst = run_ranks(_reduce_check_body, world, args=(fused, reduce_mode), backend="nccl", timeout=600)
     assert max(worst) < 1e-5, worst

@@ -38,7 +38,7 @@ from ..utils import (
     prepare_muon_grads,
     wait_group_muon_grads,
 )
-from .newton_schulz import NewtonSchulz
+from .newton_schulz import NewtonSchulz, apply_gram_factors, gram_newton_schulz_factors
 
 try:
     from torch.distributed.tensor import DTensor
@@ -453,8 +453,20 @@ class Muon(torch.optim.Optimizer):
         for dp in self._bucket_all_dps.get(gi, ()):
             if dp.tp_group is not None:
                 dp._tp_wd_factor = 1.0 - lr * wd
+        gram_ids: set[int] = set()
+        if self.tp_distributed_gram:
+            gram_dps = [
+                dp for dp in self._bucket_dps.get(gi, ())
+                if dp.tp_group is not None and dp._reduced_grad is not None and self._tp_gram_rejection_reason(dp) is None
+            ]
+            if gram_dps:
+                with prof.phase("tp_distributed_gram"):
+                    self._step_tp_distributed_gram(gram_dps, lr, mu, wd, gscale)
+                gram_ids = {id(dp) for dp in gram_dps}
         work = []
         for dp in self._bucket_dps.get(gi, ()):
+            if id(dp) in gram_ids:
+                continue
             if dp.tp_group is not None:
                 if not dp.is_tp_owner or dp._tp_full_grad is None:
                     continue
@@ -498,6 +510,107 @@ class Muon(torch.optim.Optimizer):
         if wd > 0:
             w.mul_(1.0 - lr * wd)
         w.add_(upd.to(w.dtype), alpha=-lr * scale)
+
+    # ------------------------------------------------------------------ TP distributed Gram
+    def _tp_gram_segment_count(self) -> int:
+        coefs = self.ns.resolved_coefficients(self.ns_steps)
+        return 1 + sum(1 for i in self.ns.resolved_restarts() if i != 0 and 0 <= i < len(coefs))
+
+    def _tp_gram_wire_dtype(self) -> torch.dtype:
+        return torch.float16 if self.device.type == "cuda" else torch.float32
+
+    def _tp_gram_rejection_reason(self, dp) -> Optional[str]:
+        """Why a parameter keeps the gather -> NS -> scatter route (None: it
+        takes the factor-broadcast route).  Same rules as the reference
+        (``dmuon/optim/muon.py:1035-1078``): Gram formulation only, the shard
+        must lie along the columns of the oriented (wide) matrix so that the
+        factors multiply from the left, and under the default policy the
+        factors must be clearly cheaper to send than the full update."""
+        if self.ns.backend != "gram":
+            return "non_gram_backend"
+        if dp.tp_group is None:
+            return "non_tp_param"
+        if dp.shard_dim not in (0, 1):
+            return "unsupported_shard_dim"
+        if len(dp.full_shape) < 2:
+            return "not_matrix"
+        rows = int(dp.full_shape[0])
+        cols = int(math.prod(dp.full_shape[1:]))
+        transposed = rows > cols
+        if (1 - dp.shard_dim if transposed else dp.shard_dim) != 1:
+            return "unsupported_orientation"
+        policy = str(self.tp_distributed_gram_policy).lower()
+        if policy in ("all", "force", "always"):
+            return None
+        if policy in ("0", "false", "no", "off", "none"):
+            return "policy_disabled"
+        factor_dim = cols if transposed else rows
+        scatter_bytes = rows * cols * dp._owned_data.element_size()
+        factor_bytes = self._tp_gram_segment_count() * factor_dim * factor_dim * 2
+        ratio = self.tp_distributed_gram_max_factor_to_scatter_ratio
+        if ratio <= 0:
+            return "ratio_threshold_disabled"
+        if factor_bytes >= scatter_bytes:
+            return "factor_not_smaller"
+        if factor_bytes / scatter_bytes > ratio:
+            return "factor_ratio_too_high"
+        return None
+
+    def _step_tp_distributed_gram(self, dps, lr, mu, wd, gscale) -> None:
+        """TP owners turn the gathered full matrix into left-factor segments
+        and broadcast them (plus the normaliser); every TP rank keeps momentum
+        for its own shard and applies the factors to it, so the full update is
+        never scattered (reference ``dmuon/optim/muon.py:1097-1278``)."""
+        nseg, wire = self._tp_gram_segment_count(), self._tp_gram_wire_dtype()
+        pending = []
+        for dp in dps:
+            st = self.state[id(dp)]
+            rows = int(dp.full_shape[0])
+            cols = int(math.prod(dp.full_shape[1:]))
+            transposed = rows > cols
+            fdim = cols if transposed else rows
+            lg = _local(dp._reduced_grad)
+            lg = lg.reshape(lg.shape[0], -1).to(dp._optim_dtype)
+            if gscale is not None:
+                lg = lg * gscale.to(lg.dtype)
+            lbuf = st.get("tp_local_momentum_buffer")
+            if lbuf is None:
+                lbuf = st["tp_local_momentum_buffer"] = torch.zeros_like(lg)
+            lbuf.mul_(mu).add_(lg)
+            local_u = lg.add(lbuf, alpha=mu) if self.nesterov else lbuf
+            if dp.is_tp_owner:
+                if dp._tp_full_grad is None:
+                    raise RuntimeError(f"{dp.param_name}: the TP gather did not deliver the full gradient to its TP owner")
+                fg = dp._tp_full_grad.reshape(rows, cols).to(dp._optim_dtype)
+                if gscale is not None:
+                    fg = fg * gscale.to(fg.dtype)
+                fbuf = self._momentum_of(dp, (rows, cols), fg.device)
+                fbuf.mul_(mu).add_(fg)
+                full_u = fg.add(fbuf, alpha=mu) if self.nesterov else fbuf
+                segs, tr, norm = gram_newton_schulz_factors(
+                    full_u, steps=self.ns_steps, coefficients=self.ns.coefficients,
+                    restart_iterations=self.ns.restart_iterations, compute_dtype=wire,
+                )
+                assert tr == transposed and len(segs) == nseg
+                segs = [s.to(wire).contiguous() for s in segs]
+                norm = norm.reshape(()).float()
+            else:
+                segs = [torch.empty(fdim, fdim, dtype=wire, device=self.device) for _ in range(nseg)]
+                norm = torch.empty((), dtype=torch.float32, device=self.device)
+            pending.append((dp, segs, norm, local_u, transposed, rows, cols))
+        # one pass of broadcasts per TP group, in parameter order (identical on every TP rank)
+        for dp, segs, norm, *_ in pending:
+            dist.broadcast(norm, src=dp._tp_owner_global_rank, group=dp.tp_group)
+            for s in segs:
+                dist.broadcast(s, src=dp._tp_owner_global_rank, group=dp.tp_group)
+        for dp, segs, norm, local_u, transposed, rows, cols in pending:
+            upd = apply_gram_factors(local_u.float(), segs, transposed, norm)
+            w = dp._owned_data
+            if wd > 0:
+                w.mul_(1.0 - lr * wd)
+            w.add_(upd.reshape(w.shape).to(w.dtype), alpha=-lr * muon_update_scale((rows, cols)))
+            dp._tp_full_grad = dp._tp_full_delta = dp._reduced_grad = None
+            dp._tp_wd_factor = 1.0
 
     def _step_muon_kernels(self, work, lr, mu, wd, gscale) -> None:
         from ..ops import ns_sm100

@@ -92,7 +92,7 @@ def _body(rank, world, mode, steps):
     model = Net()
     for blk in model.layers:
         parallelize_module(blk, mesh["tp"], {"up_proj": ColwiseParallel(), "down_proj": RowwiseParallel()})
-    if mode == "fsdp":
+    if mode in ("fsdp", "fsdp_gram"):
         owners = dmuon.dedicate_params(model, mesh["dp"], _pred, reshard_after_forward=False)
         for blk in model.layers:
             fully_shard(blk, mesh=mesh["dp"])
@@ -100,7 +100,11 @@ def _body(rank, world, mode, steps):
     else:
         owners = dmuon.dedicate_params_ddp_tp(model, mesh["dp"], _pred)
         dmuon.replicate_tp(model, mesh["dp"])
-    opt = dmuon.Muon(model, lr=LR, momentum=MU, weight_decay=WD, adamw_lr=ALR)
+    extra = dict(tp_distributed_gram=True, tp_distributed_gram_policy="all") if mode == "fsdp_gram" else {}
+    opt = dmuon.Muon(model, lr=LR, momentum=MU, weight_decay=WD, adamw_lr=ALR, **extra)
+    if mode == "fsdp_gram":
+        # both orientations qualify: column-parallel tall and row-parallel wide matrices
+        assert all(opt._tp_gram_rejection_reason(p) is None for p in dmuon.get_dedicated_params(model))
     dp_rank = mesh["dp"].get_local_rank()
     losses = []
     for s in range(steps):
@@ -120,7 +124,7 @@ def _body(rank, world, mode, steps):
     return losses, sd, tp_owned, mshape
 
 
-@pytest.mark.parametrize("mode", ["fsdp", "ddp_tp"])
+@pytest.mark.parametrize("mode", ["fsdp", "ddp_tp", "fsdp_gram"])
 def test_tp_muon_matches_single_process(mode):
     steps = 4
     ref_losses, ref_params = _oracle(steps)

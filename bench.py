@@ -70,6 +70,8 @@ def parse_args():
                     help="pull each dedicated Linear weight inside its first forward GEMM (peer data plane only)")
     ap.add_argument("--attention", choices=("cudnn", "flash"), default="cudnn",
                     help="SDPA backend preference of this package's model (the reference arm uses Hugging Face's default)")
+    ap.add_argument("--plain-model-ops", action="store_true",
+                    help="plain PyTorch SwiGLU / rotary embedding / cross-entropy instead of this package's fused kernels")
     return ap.parse_args()
 
 
@@ -185,6 +187,7 @@ def build_ours(args, dims, rank, world, device):
     from dmuon_b200.models.llama import LlamaConfig, LlamaModel
 
     llama_mod.ATTENTION_BACKEND = args.attention
+    llama_mod.FUSED_OPS = not args.plain_model_ops
     if args.fused_publish:
         os.environ["DMUON_FUSED_PUBLISH"] = "1"
     if args.model == "pi0":
@@ -449,6 +452,8 @@ def run(args):
                 "dedicated_data_plane": getattr(args, "comm_used", "nccl")
                 + (" + publish fused into forward GEMMs" if args.fused_publish else ""),
                 "attention": (args.attention + " SDPA backend" if args.impl == "ours" else "Hugging Face sdpa default"),
+                "model_ops": ("n/a" if args.impl != "ours" else
+                              "plain PyTorch" if args.plain_model_ops else "fused SwiGLU / RoPE / linear-cross-entropy kernels"),
                 "activation_checkpointing": bool(args.act_ckpt),
                 "l2": "per-step working set (weights + activations, tens of GB) is far larger than the 126 MB L2",
             },

@@ -18,6 +18,13 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ..ops import model_ops
+
+#: Use the fused kernels (rotary embedding in place on the projection outputs,
+#: one-pass SwiGLU, linear + cross-entropy with in-chunk gradients) for CUDA
+#: tensors.  False keeps the plain PyTorch formulation everywhere.
+FUSED_OPS = True
+
 
 @dataclass
 class LlamaConfig:
@@ -86,6 +93,24 @@ def rope_tables(seq_len: int, head_dim: int, theta: float, device, dtype=torch.f
     return ang.cos().to(dtype), ang.sin().to(dtype)
 
 
+class RopeTables:
+    """fp32 position tables handed from the model to its layers.  A plain
+    object rather than tensors in the argument list: wrappers that cast
+    floating-point forward inputs to the compute dtype (FSDP2 mixed precision)
+    leave it alone, so the rotation keeps fp32 angles."""
+
+    def __init__(self, cos: torch.Tensor, sin: torch.Tensor):
+        self.cos, self.sin = cos, sin
+        self._cast: dict = {}
+
+    def as_dtype(self, dtype: torch.dtype) -> tuple[torch.Tensor, torch.Tensor]:
+        if dtype == self.cos.dtype:
+            return self.cos, self.sin
+        if dtype not in self._cast:
+            self._cast[dtype] = (self.cos.to(dtype), self.sin.to(dtype))
+        return self._cast[dtype]
+
+
 def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
     # x: [B, H, S, D]; rotate-half convention
     d = x.shape[-1] // 2
@@ -119,13 +144,19 @@ class Attention(nn.Module):
         self.v_proj = nn.Linear(cfg.d_model, cfg.n_kv_heads * cfg.head_dim, bias=False)
         self.o_proj = nn.Linear(cfg.n_heads * cfg.head_dim, cfg.d_model, bias=False)
 
-    def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, rope: RopeTables) -> torch.Tensor:
         b, s, _ = x.shape
-        q = self.q_proj(x).view(b, s, self.n_heads, self.hd).transpose(1, 2)
-        k = self.k_proj(x).view(b, s, self.n_kv, self.hd).transpose(1, 2)
+        q, k = self.q_proj(x), self.k_proj(x)
         v = self.v_proj(x).view(b, s, self.n_kv, self.hd).transpose(1, 2)
-        q = apply_rope(q, cos, sin)
-        k = apply_rope(k, cos, sin)
+        if FUSED_OPS and q.is_cuda:
+            # rotated in place, in the [b, s, h, d] layout the projections wrote
+            q, k = model_ops.rope_qk_(q, k, rope.cos, rope.sin, self.hd)
+            q = q.view(b, s, self.n_heads, self.hd).transpose(1, 2)
+            k = k.view(b, s, self.n_kv, self.hd).transpose(1, 2)
+        else:
+            cos, sin = rope.as_dtype(q.dtype)
+            q = apply_rope(q.view(b, s, self.n_heads, self.hd).transpose(1, 2), cos, sin)
+            k = apply_rope(k.view(b, s, self.n_kv, self.hd).transpose(1, 2), cos, sin)
         o = causal_attention(q, k, v, self.n_kv != self.n_heads)
         return self.o_proj(o.transpose(1, 2).reshape(b, s, self.n_heads * self.hd))
 
@@ -138,7 +169,8 @@ class MLP(nn.Module):
         self.down_proj = nn.Linear(cfg.ffn_hidden, cfg.d_model, bias=False)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.down_proj(F.silu(self.gate_proj(x)) * self.up_proj(x))
+        g, u = self.gate_proj(x), self.up_proj(x)
+        return self.down_proj(model_ops.swiglu(g, u) if FUSED_OPS else F.silu(g) * u)
 
 
 class DecoderLayer(nn.Module):
@@ -149,8 +181,8 @@ class DecoderLayer(nn.Module):
         self.post_attention_layernorm = RMSNorm(cfg.d_model, cfg.norm_eps)
         self.mlp = MLP(cfg)
 
-    def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
-        x = x + self.self_attn(self.input_layernorm(x), cos, sin)
+    def forward(self, x: torch.Tensor, rope: RopeTables) -> torch.Tensor:
+        x = x + self.self_attn(self.input_layernorm(x), rope)
         return x + self.mlp(self.post_attention_layernorm(x))
 
 
@@ -181,9 +213,9 @@ class LlamaModel(nn.Module):
 
     def hidden(self, input_ids: torch.Tensor) -> torch.Tensor:
         x = self.embed_tokens(input_ids)
-        cos, sin = rope_tables(input_ids.shape[1], self.cfg.head_dim, self.cfg.rope_theta, x.device, x.dtype)
+        rope = RopeTables(*rope_tables(input_ids.shape[1], self.cfg.head_dim, self.cfg.rope_theta, x.device))
         for layer in self.layers:
-            x = layer(x, cos, sin)
+            x = layer(x, rope)
         return self.norm(x)
 
     def forward(self, input_ids: torch.Tensor, labels: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -196,6 +228,8 @@ class LlamaModel(nn.Module):
         h2 = h.reshape(-1, h.shape[-1])
         y = labels.reshape(-1)
         chunk = self.cfg.loss_chunk
+        if FUSED_OPS and h2.is_cuda and model_ops.kernels_apply(h2) and self.lm_head.weight.dtype == h2.dtype:
+            return model_ops.linear_cross_entropy(h2, self.lm_head.weight, y, chunk)
         if chunk <= 0 or h2.shape[0] <= chunk:
             return F.cross_entropy(self.lm_head(h2).float(), y)
         total = h2.new_zeros((), dtype=torch.float32)

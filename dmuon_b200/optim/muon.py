@@ -399,6 +399,8 @@ class Muon(torch.optim.Optimizer):
         for g in groups:
             if g.mode == "fsdp" and (g._is_unsharded or g._unshard_ticket is not None):
                 g.reshard()
+            if g.mode == "fsdp":
+                g.stage_publish_targets()
 
         with prof.phase("muon"):
             for gi, pg in enumerate(self.param_groups):

@@ -240,6 +240,28 @@ class DedicatedParamGroup:
             free_storage(p._flat_full)
         self._is_unsharded = False
 
+    def stage_publish_targets(self) -> None:
+        """Called right before the optimizer step: bring back the storage of
+        this rank's own packed publish buffer and tell its Muon parameters
+        where their slot is, so the update kernel that writes the fp32 master
+        also leaves the bf16 copy there and the next ``unshard`` has nothing
+        to copy in (the reference always re-casts every owned master before
+        each forward, ``dmuon/_backends/fsdp2/group.py:767-781``)."""
+        if self.mode != "fsdp" or self.device.type != "cuda":
+            return
+        buf = self._packed.get(self.shard_rank)
+        if buf is None or buf.dtype != torch.bfloat16:
+            return
+        targets = [
+            p for p in self._pub_by_shard[self.shard_rank]
+            if p.is_owner and p._dmuon_route == "muon" and p.tp_group is None
+        ]
+        if not targets:
+            return
+        alloc_storage(buf)
+        for p in targets:
+            p._publish_view = buf[p._packed_offset : p._packed_offset + p.numel].view(p._orig_size)
+
     # ------------------------------------------------------------------ reduce
     def _grad_dtype_of(self, p: DedicatedParam, g: torch.Tensor) -> torch.dtype:
         return p._grad_dtype or g.dtype
@@ -274,9 +296,22 @@ class DedicatedParamGroup:
 
         packs: list[_PackedGrad] = []
         with torch.no_grad():
+            alone = self.shard_size == 1 and self.replicate_size == 1
             for coord in sorted(by_coord):
                 items = by_coord[coord]
                 dtype = self._grad_dtype_of(*items[0])
+                if alone:
+                    # nothing travels: the autograd buffers themselves are the reduced gradients
+                    direct = [
+                        (p, g) for p, g in items
+                        if p._accumulated_grad is None and g.dtype == dtype and g.is_contiguous()
+                    ]
+                    for p, g in direct:
+                        packs.append(_PackedGrad(coord, [p], g.detach().reshape(-1), [0]))
+                        p.clear_local_grad()
+                    items = [(p, g) for p, g in items if all(p is not q for q, _ in direct)]
+                    if not items:
+                        continue
                 total = sum(p.numel for p, _ in items)
                 buf = torch.empty(total, dtype=dtype, device=self.device)
                 offs, off = [], 0

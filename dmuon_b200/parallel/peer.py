@@ -395,6 +395,10 @@ class PeerParamGroup(DedicatedParamGroup):
         # slots live in the runtime's arenas; PeerRuntime wires them after all groups exist
         return
 
+    def stage_publish_targets(self) -> None:
+        # publish slots are fixed arena views, wired once by the runtime
+        return
+
     def unshard(self, prefetch: bool = False) -> None:
         if self._is_unsharded or self._unshard_ticket is not None:
             return

@@ -162,6 +162,13 @@ def _load_dedicated(dp, full: torch.Tensor) -> None:
     if dp._owned_data is not None:
         dp._owned_data.copy_(local)
         dp._publish_fresh = False
+    if dp._sharded_muon_data is not None:
+        per = dp._flat_shard_numel
+        flat = local.reshape(-1)
+        lo = min(dp.numel, dp.shard_rank * per)
+        hi = min(dp.numel, lo + per)
+        dp._sharded_muon_data.zero_()
+        dp._sharded_muon_data[: hi - lo].copy_(flat[lo:hi])
     if dp.mode == "ddp":
         dp.copy_owned_to_live()
 

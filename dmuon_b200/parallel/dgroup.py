@@ -106,8 +106,12 @@ class DedicatedParamGroup:
         self.replicate_rank = self.replicate_group.rank() if self.replicate_group is not None else 0
         self.replicate_size = self.replicate_group.size() if self.replicate_group is not None else 1
 
-        self.bcast_params = [p for p in self.params if p._dmuon_route != "sharded_adamw"]
-        self.flat_params = [p for p in self.params if p._dmuon_route == "sharded_adamw"]
+        # forward copy rebuilt by all-gather from per-rank shards / by broadcast from the owner
+        self.flat_params = [
+            p for p in self.params if p._dmuon_route == "sharded_adamw" or p._sharded_muon_data is not None
+        ]
+        self.bcast_params = [p for p in self.params if all(p is not q for q in self.flat_params)]
+        self.gather_muon_params = [p for p in self.flat_params if p._sharded_muon_data is not None]
         self.tp_params = [p for p in self.params if p.tp_group is not None]
 
         self._is_unsharded = False
@@ -205,7 +209,7 @@ class DedicatedParamGroup:
         self._prefetched = prefetch
 
     def _all_gather_flat(self, p: DedicatedParam) -> None:
-        shard = p._sharded_adamw_data.to(p._param_dtype)
+        shard = p.forward_shard().to(p._param_dtype)
         if self.shard_size > 1:
             dist.all_gather_into_tensor(p._flat_full, shard, group=self.dp_group)
         else:
@@ -498,7 +502,10 @@ class DedicatedParamGroup:
     def _replicate_publish_params(self) -> list[DedicatedParam]:
         if self.replicate_size <= 1:
             return []
-        return [p for p in self.bcast_params if p.in_owner_column and p._owned_data is not None]
+        return [
+            p for p in self.params
+            if p._dmuon_route != "sharded_adamw" and p.in_owner_column and p._owned_data is not None
+        ]
 
     def replicate_broadcast_sync(self) -> None:
         self.replicate_broadcast_async()
@@ -547,6 +554,37 @@ class DedicatedParamGroup:
         if t is not None:
             self._tp_ticket = t
         self.replicate_broadcast_async()
+        self.sharded_muon_publish_async()
+
+    def sharded_muon_publish_async(self) -> None:
+        """"all_gather" Muon placement: after the update every rank of the owner's
+        shard column holds the new master (the owner computed it, its replicas
+        received it on the replicate axis); each of them scatters the compute-
+        dtype copy over its shard group, so every rank ends up with the slice it
+        contributes to the next forward all-gather.  Same result as the
+        reference's reduce-scatter of zeros (``dmuon/_backends/fsdp2/group.py:
+        1882-2013``) with a plain scatter as the collective."""
+        plist = self.gather_muon_params
+        if not plist:
+            return
+        ctx = self.comm_ctx
+        lane = ctx.replicate_broadcast_lane
+        lane.follow_current()
+        with lane.use(), torch.no_grad():
+            with ctx.time_region("post_step", self.name, "sharded_muon_publish", lane):
+                for p in plist:
+                    per, n = p._flat_shard_numel, self.shard_size
+                    src = self._global_rank(self.dp_group, p.owner_shard)
+                    if p.in_owner_column:
+                        padded = torch.zeros(per * n, dtype=p._param_dtype, device=self.device)
+                        padded[: p.numel].copy_(p._owned_data.reshape(-1))
+                        pieces = list(padded.chunk(n))
+                        lane.keep_alive(padded)
+                    else:
+                        pieces = None
+                    lane.keep_alive(p._sharded_muon_data)
+                    dist.scatter(p._sharded_muon_data, scatter_list=pieces, src=src, group=self.dp_group)
+        self._post_step_ticket = lane.mark()
 
     def _pre_forward_wait(self) -> None:
         """Consume the previous step's asynchronous publish before reading masters."""

@@ -148,6 +148,7 @@ class DedicatedParam:
         self._tp_wd_factor: float = 1.0
         self._sharded_adamw_grad: Optional[torch.Tensor] = None
         self._sharded_adamw_data: Optional[torch.Tensor] = None
+        self._sharded_muon_data: Optional[torch.Tensor] = None   # forward shard of the "all_gather" Muon placement
         self._publish_fresh = False      # published copy already equals the master copy
 
         self._original_param = param
@@ -169,6 +170,8 @@ class DedicatedParam:
             self._init_flat_shard(local)
         elif self.in_owner_column:
             self._owned_data = local.detach().to(device=self.device, dtype=self._master_dtype).clone()
+        if self.uses_sharded_muon_forward():
+            self._sharded_muon_data = self._flat_shard_of(local, self._param_dtype)
         self._placeholder = nn.Parameter(
             torch.empty(0, dtype=self._orig_dtype, device=self.device), requires_grad=self._requires_grad
         )
@@ -180,16 +183,34 @@ class DedicatedParam:
         if not self.is_dtensor and local.device == self.device:
             free_storage(local)
 
-    def _init_flat_shard(self, local: torch.Tensor) -> None:
+    def uses_sharded_muon_forward(self) -> bool:
+        """Muon route whose forward copy is rebuilt by all-gather from per-rank
+        shards instead of a broadcast from the owner (the reference's
+        experimental ``muon_forward_unshard="all_gather"``,
+        dmuon/_backends/fsdp2/param.py:316-325)."""
+        return (
+            self.mode == "fsdp" and self._dmuon_route == "muon" and self._muon_forward_unshard == "all_gather"
+            and self.tp_group is None and self.shard_size > 1
+        )
+
+    def _flat_shard_of(self, local: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+        """This rank's zero-padded slice of the flattened tensor."""
         n = self.shard_size
         per = (self.numel + n - 1) // n
         self._flat_shard_numel = per
-        flat = local.detach().to(device=self.device, dtype=self._master_dtype).reshape(-1)
+        flat = local.detach().reshape(-1)
         lo = min(self.numel, self.shard_rank * per)
         hi = min(self.numel, lo + per)
-        shard = torch.zeros(per, dtype=self._master_dtype, device=self.device)
+        shard = torch.zeros(per, dtype=dtype, device=self.device)
         shard[: hi - lo].copy_(flat[lo:hi])
-        self._sharded_adamw_data = shard
+        return shard
+
+    def _init_flat_shard(self, local: torch.Tensor) -> None:
+        self._sharded_adamw_data = self._flat_shard_of(local, self._master_dtype)
+
+    def forward_shard(self) -> torch.Tensor:
+        """What this rank contributes to the forward all-gather."""
+        return self._sharded_adamw_data if self._dmuon_route == "sharded_adamw" else self._sharded_muon_data
 
     def _init_ddp(self, param: nn.Parameter, local: torch.Tensor) -> None:
         self._owned_data = local.detach().to(device=self.device, dtype=self._master_dtype).clone()

@@ -60,6 +60,8 @@ def peer_backend_possible(device: torch.device, dp_group, replicate_group, dpara
         return "tensor-parallel parameters"
     if any(p._dmuon_route == "sharded_adamw" for p in dparams):
         return "sharded_adamw route"
+    if any(p._sharded_muon_data is not None for p in dparams):
+        return "all_gather forward placement"
     if len({p._param_dtype for p in dparams}) != 1 or len({p._grad_dtype or p._param_dtype for p in dparams}) != 1:
         return "mixed publish or gradient dtypes"
     try:

@@ -15,9 +15,12 @@ def _setup(rank, world, mode, reshard=False):
     import dmuon_b200 as dmuon
 
     model = _build_model()
+    # "*_gather": Muon matrices rebuilt in forward by all-gather from per-rank shards
+    extra = dict(muon_forward_unshard="all_gather") if mode.endswith("_gather") else {}
+    mode = mode.replace("_gather", "")
     if mode == "hsdp":
         mesh = init_device_mesh("cpu", (2, world // 2), mesh_dim_names=("replicate", "shard"))
-        dmuon.dedicate_params(model, mesh["shard"], _pred, reshard_after_forward=reshard, replicate_mesh=mesh["replicate"])
+        dmuon.dedicate_params(model, mesh["shard"], _pred, reshard_after_forward=reshard, replicate_mesh=mesh["replicate"], **extra)
         for layer in model.layers:
             fully_shard(layer, mesh=mesh)
         fully_shard(model, mesh=mesh)
@@ -27,7 +30,9 @@ def _setup(rank, world, mode, reshard=False):
         dmuon.replicate(model, mesh)
     else:
         mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("dp",))
-        dmuon.dedicate_params(model, mesh, _pred, reshard_after_forward=reshard)
+        dmuon.dedicate_params(model, mesh, _pred, reshard_after_forward=reshard, **extra)
+        if extra:
+            assert all(p._sharded_muon_data is not None for p in dmuon.get_dedicated_params(model))
         for layer in model.layers:
             fully_shard(layer, mesh=mesh)
         fully_shard(model, mesh=mesh)
@@ -65,7 +70,10 @@ def _body_mode(rank, world, mode, reshard, steps):
     return losses, sd, plan["owner_imbalance"], len(groups)
 
 
-@pytest.mark.parametrize("mode,reshard", [("fsdp", False), ("hsdp", False), ("hsdp", True), ("ddp", False)])
+@pytest.mark.parametrize(
+    "mode,reshard",
+    [("fsdp", False), ("hsdp", False), ("hsdp", True), ("ddp", False), ("fsdp_gather", True), ("hsdp_gather", False)],
+)
 def test_four_rank_placements_match_single_process(mode, reshard):
     steps = 5
     ref_losses, ref_params = oracle_run(steps)
@@ -123,7 +131,7 @@ def _body_ckpt(rank, world, mode):
     return cont, cont2, keys, tuple(mom.shape), str(mom.dtype), sorted(msd)
 
 
-@pytest.mark.parametrize("mode", ["fsdp", "hsdp", "ddp"])
+@pytest.mark.parametrize("mode", ["fsdp", "hsdp", "ddp", "fsdp_gather"])
 def test_checkpoint_roundtrip_resumes_identically(mode):
     world = 4 if mode == "hsdp" else 2
     res = run_ranks(_body_ckpt, world, args=(mode,))

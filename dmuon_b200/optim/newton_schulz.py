@@ -346,10 +346,20 @@ class NewtonSchulz:
         """Orthogonalise one full matrix."""
         if self.uses_kernels(G):
             from ..ops import ns_sm100
+            from . import ns_graph
 
-            return ns_sm100.newton_schulz_single(
-                G, self.resolved_coefficients(steps), self.resolved_restarts(), 1e-7, self.backend, self.compute_dtype
-            )
+            coefs, restarts = self.resolved_coefficients(steps), self.resolved_restarts()
+
+            def run(x: Tensor) -> Tensor:
+                return ns_sm100.newton_schulz_single(x, coefs, restarts, 1e-7, self.backend, self.compute_dtype)
+
+            if ns_graph.enabled() and not torch.cuda.is_current_stream_capturing():
+                key = (
+                    tuple(G.shape), G.dtype, G.device.index, self.backend, self.compute_dtype,
+                    tuple(map(tuple, coefs)), tuple(restarts),
+                )
+                return ns_graph.cache().run(key, run, G)
+            return run(G)
         if self.backend == "gram":
             return gram_newton_schulz(
                 G,
@@ -381,8 +391,11 @@ def get_ns_backend() -> str:
 def get_backend_status() -> dict:
     from ..ops import build as _build
     from ..ops import ns_sm100
+    from . import ns_graph
 
     return {
+        "cuda_graph_replay": ns_graph.enabled(),
+        "cuda_graph_cache": ns_graph.cache().stats(),
         "ns_backend": get_ns_backend(),
         "formulation": _ACTIVE["backend"],
         "arch": "sm_100a",

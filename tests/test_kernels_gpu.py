@@ -299,3 +299,27 @@ def test_muon_update_batched_matches_reference_math(cdt):
         upd_err = (masters[i] - ref).abs().max().item()
         assert upd_err < 0.1 * lr * scale, upd_err
         assert (pubs[i].float() - masters[i]).abs().max().item() < 1e-2 * masters[i].abs().max().item()
+
+
+def test_newton_schulz_graph_replay_matches_eager(monkeypatch):
+    """Stand-alone NS through the CUDA-graph cache: eager on the first call,
+    captured on the second, replayed afterwards, same numbers as eager."""
+    import dmuon_b200 as dmuon
+    from dmuon_b200.optim import ns_graph
+
+    dev = torch.device("cuda", 0)
+    ns = dmuon.NewtonSchulz()
+    torch.manual_seed(11)
+    mats = [torch.randn(384, 1024, device=dev) for _ in range(4)]
+    monkeypatch.setenv("DMUON_NS_CUDA_GRAPH", "0")
+    eager = [ns.local(m, 5).clone() for m in mats]
+    monkeypatch.setenv("DMUON_NS_CUDA_GRAPH", "1")
+    ns_graph.cache().clear()
+    base = ns_graph.cache().stats()
+    got = [ns.local(m, 5).clone() for m in mats]
+    torch.cuda.synchronize()
+    st = ns_graph.cache().stats()
+    assert st["failed"] == 0 and st["captures"] - base["captures"] == 1 and st["replays"] - base["replays"] == 3
+    for a, b in zip(got, eager):
+        assert torch.equal(a, b)
+    assert dmuon.get_backend_status()["cuda_graph_replay"] is True

@@ -32,7 +32,9 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .llama import RMSNorm, apply_rope, rope_tables
+from ..ops import model_ops
+from . import llama as _llama
+from .llama import RMSNorm, RopeTables, apply_rope, rope_tables
 
 
 @dataclass
@@ -139,19 +141,27 @@ class GemmaAttnMLP(nn.Module):
         self.up_proj = nn.Linear(width, ffn, bias=False)
         self.down_proj = nn.Linear(ffn, width, bias=False)
 
-    def qkv(self, x, cos, sin):
+    def qkv(self, x, rope: RopeTables):
         b, s, _ = x.shape
         h = self.input_layernorm(x)
-        q = apply_rope(self.q_proj(h).view(b, s, self.h, self.hd).transpose(1, 2), cos, sin)
-        k = apply_rope(self.k_proj(h).view(b, s, self.kv, self.hd).transpose(1, 2), cos, sin)
+        q, k = self.q_proj(h), self.k_proj(h)
         v = self.v_proj(h).view(b, s, self.kv, self.hd).transpose(1, 2)
+        if _llama.FUSED_OPS and q.is_cuda:
+            q, k = model_ops.rope_qk_(q, k, rope.cos, rope.sin, self.hd)
+            q = q.view(b, s, self.h, self.hd).transpose(1, 2)
+            k = k.view(b, s, self.kv, self.hd).transpose(1, 2)
+        else:
+            cos, sin = rope.as_dtype(q.dtype)
+            q = apply_rope(q.view(b, s, self.h, self.hd).transpose(1, 2), cos, sin)
+            k = apply_rope(k.view(b, s, self.kv, self.hd).transpose(1, 2), cos, sin)
         return q, k, v
 
     def finish(self, x, attn):
         b, s, _ = x.shape
         x = x + self.o_proj(attn.transpose(1, 2).reshape(b, s, self.h * self.hd))
         h = self.post_attention_layernorm(x)
-        return x + self.down_proj(F.gelu(self.gate_proj(h), approximate="tanh") * self.up_proj(h))
+        g, u = self.gate_proj(h), self.up_proj(h)
+        return x + self.down_proj(model_ops.geglu(g, u) if _llama.FUSED_OPS else F.gelu(g, approximate="tanh") * u)
 
 
 class JointLayer(nn.Module):
@@ -165,8 +175,8 @@ class JointLayer(nn.Module):
         self.expert = GemmaAttnMLP(c.expert_width, c.expert_ffn, c)
 
     def forward(self, xp, xa, rope_p, rope_a):
-        qp, kp, vp = self.backbone.qkv(xp, *rope_p)
-        qa, ka, va = self.expert.qkv(xa, *rope_a)
+        qp, kp, vp = self.backbone.qkv(xp, rope_p)
+        qa, ka, va = self.expert.qkv(xa, rope_a)
         gqa = self.backbone.kv != self.backbone.h
         if not self.last:
             # the prefix stream of the last layer feeds nothing: only its keys and values are used
@@ -220,8 +230,8 @@ class Pi0Model(nn.Module):
         a_tok = self.time_mlp_out(F.silu(self.time_mlp_in(torch.cat((a_tok, temb), dim=-1))))
         xa = torch.cat((self.state_in(state.to(xp.dtype))[:, None], a_tok), dim=1)
         sp, sa = xp.shape[1], xa.shape[1]
-        cos, sin = rope_tables(sp + sa, c.head_dim, c.rope_theta, xp.device, xp.dtype)
-        rope_p, rope_a = (cos[:sp], sin[:sp]), (cos[sp:], sin[sp:])
+        cos, sin = rope_tables(sp + sa, c.head_dim, c.rope_theta, xp.device)
+        rope_p, rope_a = RopeTables(cos[:sp], sin[:sp]), RopeTables(cos[sp:], sin[sp:])
         for layer in self.layers:
             xp, xa = layer(xp, xa, rope_p, rope_a)
         return self.action_out(self.expert_norm(xa[:, 1:]))

@@ -41,8 +41,25 @@ inline int grid_for(long long work_items) {
 
 __device__ __forceinline__ float sigmoidf_fast(float x) { return 1.f / (1.f + __expf(-x)); }
 
+// Gate activations of the gated MLPs: value and derivative in one go.
+//   ACT 0: silu(x) = x sigmoid(x)          ACT 1: gelu, tanh approximation
+template <int ACT>
+__device__ __forceinline__ void act_and_grad(float x, float& y, float& dy) {
+  if constexpr (ACT == 0) {
+    const float s = sigmoidf_fast(x);
+    y = x * s;
+    dy = s + y * (1.f - s);
+  } else {
+    const float k = 0.7978845608028654f, c = 0.044715f;
+    const float inner = k * (x + c * x * x * x);
+    const float t = 1.f - 2.f / (1.f + __expf(2.f * inner));   // tanh(inner)
+    y = 0.5f * x * (1.f + t);
+    dy = 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * k * (1.f + 3.f * c * x * x);
+  }
+}
+
 // ---------------------------------------------------------------- SwiGLU
-template <typename T>
+template <typename T, int ACT>
 __global__ void __launch_bounds__(kBlock) swiglu_fwd_kernel(const T* __restrict__ g, const T* __restrict__ u,
                                                             T* __restrict__ o, long long n) {
   const bool vec = aligned16(g) && aligned16(u) && aligned16(o);
@@ -54,17 +71,22 @@ __global__ void __launch_bounds__(kBlock) swiglu_fwd_kernel(const T* __restrict_
     load8<T>(g + i * kVec, gv);
     load8<T>(u + i * kVec, uv);
 #pragma unroll
-    for (int k = 0; k < kVec; ++k) ov[k] = gv[k] * sigmoidf_fast(gv[k]) * uv[k];
+    for (int k = 0; k < kVec; ++k) {
+      float y, dy;
+      act_and_grad<ACT>(gv[k], y, dy);
+      ov[k] = y * uv[k];
+    }
     store8<T>(o + i * kVec, ov);
   }
   for (long long i = nvec * kVec + tid; i < n; i += stride) {
-    const float gg = Conv<T>::to(g[i]);
-    o[i] = Conv<T>::from(gg * sigmoidf_fast(gg) * Conv<T>::to(u[i]));
+    float y, dy;
+    act_and_grad<ACT>(Conv<T>::to(g[i]), y, dy);
+    o[i] = Conv<T>::from(y * Conv<T>::to(u[i]));
   }
 }
 
 // dg / du may alias g / u: each thread reads its elements before writing them.
-template <typename T>
+template <typename T, int ACT>
 __global__ void __launch_bounds__(kBlock) swiglu_bwd_kernel(const T* g, const T* u, const T* __restrict__ d,
                                                             T* dg, T* du, long long n) {
   const bool vec = aligned16(g) && aligned16(u) && aligned16(d) && aligned16(dg) && aligned16(du);
@@ -78,20 +100,20 @@ __global__ void __launch_bounds__(kBlock) swiglu_bwd_kernel(const T* g, const T*
     load8<T>(d + i * kVec, dv);
 #pragma unroll
     for (int k = 0; k < kVec; ++k) {
-      const float s = sigmoidf_fast(gv[k]);
-      const float silu = gv[k] * s;
-      a[k] = dv[k] * uv[k] * (s + silu * (1.f - s));   // d silu / d g = s (1 + g (1 - s))
-      b[k] = dv[k] * silu;
+      float y, dy;
+      act_and_grad<ACT>(gv[k], y, dy);
+      a[k] = dv[k] * uv[k] * dy;
+      b[k] = dv[k] * y;
     }
     store8<T>(dg + i * kVec, a);
     store8<T>(du + i * kVec, b);
   }
   for (long long i = nvec * kVec + tid; i < n; i += stride) {
-    const float gg = Conv<T>::to(g[i]), uu = Conv<T>::to(u[i]), dd = Conv<T>::to(d[i]);
-    const float s = sigmoidf_fast(gg);
-    const float silu = gg * s;
-    dg[i] = Conv<T>::from(dd * uu * (s + silu * (1.f - s)));
-    du[i] = Conv<T>::from(dd * silu);
+    const float uu = Conv<T>::to(u[i]), dd = Conv<T>::to(d[i]);
+    float y, dy;
+    act_and_grad<ACT>(Conv<T>::to(g[i]), y, dy);
+    dg[i] = Conv<T>::from(dd * uu * dy);
+    du[i] = Conv<T>::from(dd * y);
   }
 }
 
@@ -234,26 +256,38 @@ __global__ void __launch_bounds__(kXentBlock) softmax_xent_kernel(T* logits, con
 
 using namespace dmuon;
 
-extern "C" int dmuon_swiglu_fwd(const void* gate, const void* up, void* out, long long n, int dtype, void* stream_v) {
+extern "C" int dmuon_swiglu_fwd(const void* gate, const void* up, void* out, long long n, int act, int dtype,
+                                void* stream_v) {
   if (n <= 0) return 0;
+  if (act != 0 && act != 1) return -22;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_v);
   const int grid = grid_for((n + kVec - 1) / kVec);
   DMUON_MODEL_DISPATCH(dtype, T,
-    swiglu_fwd_kernel<T><<<grid, kBlock, 0, st>>>(static_cast<const T*>(gate), static_cast<const T*>(up),
-                                                  static_cast<T*>(out), n));
+    if (act == 0)
+      swiglu_fwd_kernel<T, 0><<<grid, kBlock, 0, st>>>(static_cast<const T*>(gate), static_cast<const T*>(up),
+                                                       static_cast<T*>(out), n);
+    else
+      swiglu_fwd_kernel<T, 1><<<grid, kBlock, 0, st>>>(static_cast<const T*>(gate), static_cast<const T*>(up),
+                                                       static_cast<T*>(out), n));
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }
 
 extern "C" int dmuon_swiglu_bwd(const void* gate, const void* up, const void* d_out, void* d_gate, void* d_up,
-                                long long n, int dtype, void* stream_v) {
+                                long long n, int act, int dtype, void* stream_v) {
   if (n <= 0) return 0;
+  if (act != 0 && act != 1) return -22;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_v);
   const int grid = grid_for((n + kVec - 1) / kVec);
   DMUON_MODEL_DISPATCH(dtype, T,
-    swiglu_bwd_kernel<T><<<grid, kBlock, 0, st>>>(static_cast<const T*>(gate), static_cast<const T*>(up),
-                                                  static_cast<const T*>(d_out), static_cast<T*>(d_gate),
-                                                  static_cast<T*>(d_up), n));
+    if (act == 0)
+      swiglu_bwd_kernel<T, 0><<<grid, kBlock, 0, st>>>(static_cast<const T*>(gate), static_cast<const T*>(up),
+                                                       static_cast<const T*>(d_out), static_cast<T*>(d_gate),
+                                                       static_cast<T*>(d_up), n);
+    else
+      swiglu_bwd_kernel<T, 1><<<grid, kBlock, 0, st>>>(static_cast<const T*>(gate), static_cast<const T*>(up),
+                                                       static_cast<const T*>(d_out), static_cast<T*>(d_gate),
+                                                       static_cast<T*>(d_up), n));
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }

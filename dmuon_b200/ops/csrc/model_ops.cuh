@@ -10,13 +10,14 @@
 
 extern "C" {
 
-// out = silu(gate) * up                                  (n elements each)
-int dmuon_swiglu_fwd(const void* gate, const void* up, void* out, long long n, int dtype, void* stream);
+// Gated MLP activation, act = 0: silu (SwiGLU), act = 1: gelu with the tanh approximation (GeGLU).
+// out = act(gate) * up                                   (n elements each)
+int dmuon_swiglu_fwd(const void* gate, const void* up, void* out, long long n, int act, int dtype, void* stream);
 
-// d_gate = d_out * up * silu'(gate) ;  d_up = d_out * silu(gate)
+// d_gate = d_out * up * act'(gate) ;  d_up = d_out * act(gate)
 // d_gate / d_up may alias gate / up (every element is read before it is written).
 int dmuon_swiglu_bwd(const void* gate, const void* up, const void* d_out, void* d_gate, void* d_up,
-                     long long n, int dtype, void* stream);
+                     long long n, int act, int dtype, void* stream);
 
 // Rotary embedding in place on q [rows, q_heads, head_dim] and k [rows,
 // k_heads, head_dim] (row = batch * seq + position; row strides in elements),

@@ -26,8 +26,8 @@ _P, _LL, _I, _F = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_flo
 @lru_cache(maxsize=None)
 def _lib():
     lib = _build.load()
-    lib.dmuon_swiglu_fwd.argtypes = [_P, _P, _P, _LL, _I, _P]
-    lib.dmuon_swiglu_bwd.argtypes = [_P, _P, _P, _P, _P, _LL, _I, _P]
+    lib.dmuon_swiglu_fwd.argtypes = [_P, _P, _P, _LL, _I, _I, _P]
+    lib.dmuon_swiglu_bwd.argtypes = [_P, _P, _P, _P, _P, _LL, _I, _I, _P]
     lib.dmuon_rope_inplace.argtypes = [_P, _P, _P, _P, _LL, _I, _I, _I, _I, _LL, _LL, _I, _I, _P]
     lib.dmuon_softmax_xent_inplace.argtypes = [_P, _P, _P, _LL, _I, _LL, _F, _I, _P]
     for name in ("dmuon_swiglu_fwd", "dmuon_swiglu_bwd", "dmuon_rope_inplace", "dmuon_softmax_xent_inplace"):
@@ -49,21 +49,29 @@ def kernels_apply(t: torch.Tensor) -> bool:
     return t.is_cuda and t.dtype in _DT
 
 
-# ---------------------------------------------------------------------------- SwiGLU
+# ---------------------------------------------------------------------------- gated MLP activations
+ACT_SILU, ACT_GELU_TANH = 0, 1
+
+
 def swiglu_reference(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return F.silu(gate) * up
 
 
-class _SwiGLU(torch.autograd.Function):
+def geglu_reference(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    return F.gelu(gate, approximate="tanh") * up
+
+
+class _GatedAct(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    def forward(ctx, gate: torch.Tensor, up: torch.Tensor, act: int) -> torch.Tensor:
         gate, up = gate.contiguous(), up.contiguous()
         out = torch.empty_like(gate)
         _check(
-            _lib().dmuon_swiglu_fwd(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel(), _DT[gate.dtype], _stream(gate)),
+            _lib().dmuon_swiglu_fwd(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel(), act, _DT[gate.dtype], _stream(gate)),
             "dmuon_swiglu_fwd",
         )
         ctx.save_for_backward(gate, up)
+        ctx.act = act
         return out
 
     @staticmethod
@@ -74,19 +82,26 @@ class _SwiGLU(torch.autograd.Function):
         _check(
             _lib().dmuon_swiglu_bwd(
                 gate.data_ptr(), up.data_ptr(), d_out.data_ptr(), d_gate.data_ptr(), d_up.data_ptr(),
-                gate.numel(), _DT[gate.dtype], _stream(gate),
+                gate.numel(), ctx.act, _DT[gate.dtype], _stream(gate),
             ),
             "dmuon_swiglu_bwd",
         )
-        return d_gate, d_up
+        return d_gate, d_up, None
 
 
 def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """``silu(gate) * up`` in one pass (three in the backward: gate, up and
     the incoming gradient are read once, both gradients written once)."""
     if kernels_apply(gate) and gate.dtype == up.dtype and gate.shape == up.shape:
-        return _SwiGLU.apply(gate, up)
+        return _GatedAct.apply(gate, up, ACT_SILU)
     return swiglu_reference(gate, up)
+
+
+def geglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """``gelu_tanh(gate) * up``, same kernels as :func:`swiglu`."""
+    if kernels_apply(gate) and gate.dtype == up.dtype and gate.shape == up.shape:
+        return _GatedAct.apply(gate, up, ACT_GELU_TANH)
+    return geglu_reference(gate, up)
 
 
 # ---------------------------------------------------------------------------- rotary embedding

@@ -320,6 +320,10 @@ def test_newton_schulz_graph_replay_matches_eager(monkeypatch):
     torch.cuda.synchronize()
     st = ns_graph.cache().stats()
     assert st["failed"] == 0 and st["captures"] - base["captures"] == 1 and st["replays"] - base["replays"] == 3
+    # The Frobenius norm is accumulated with atomics, so two runs of one input differ
+    # in the last bit of the scale and the fp16 iteration amplifies that to a few
+    # 1e-3; a replay that used a stale input or output would be off by about 1.4.
     for a, b in zip(got, eager):
-        assert torch.equal(a, b)
+        rel = ((a - b).norm() / b.norm()).item()
+        assert rel < 2e-2, rel
     assert dmuon.get_backend_status()["cuda_graph_replay"] is True

@@ -18,17 +18,21 @@ def _close(a, b, tol):
 
 @pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 6e-3), (torch.float32, 2e-6)])
 @pytest.mark.parametrize("shape", [(4, 96, 1024), (3, 1001)])
-def test_swiglu_forward_backward(dtype, tol, shape):
+@pytest.mark.parametrize("act", ["silu", "gelu_tanh"])
+def test_swiglu_forward_backward(dtype, tol, shape, act):
     from dmuon_b200.ops import model_ops
+
+    fused = model_ops.swiglu if act == "silu" else model_ops.geglu
+    plain = model_ops.swiglu_reference if act == "silu" else model_ops.geglu_reference
 
     torch.manual_seed(0)
     g = torch.randn(shape, device=_dev()).mul_(2).to(dtype).requires_grad_()
     u = torch.randn(shape, device=_dev()).to(dtype).requires_grad_()
     d = torch.randn(shape, device=_dev()).to(dtype)
-    out = model_ops.swiglu(g, u)
+    out = fused(g, u)
     out.backward(d)
     gf, uf = g.detach().float().requires_grad_(), u.detach().float().requires_grad_()
-    ref = F.silu(gf) * uf
+    ref = plain(gf, uf)
     ref.backward(d.float())
     _close(out, ref, tol)
     _close(g.grad, gf.grad, tol)

@@ -58,7 +58,7 @@ def parse_args():
     ap.add_argument("--seq", type=int, default=0)
     ap.add_argument("--micro-batch", type=int, default=0)
     ap.add_argument("--optimizer", choices=("muon", "adamw"), default="muon")
-    ap.add_argument("--parallelism", default="fsdp", help="fsdp | hsdpRxS (e.g. hsdp2x4) | ddp")
+    ap.add_argument("--parallelism", default="fsdp", help="fsdp | hsdpRxS (e.g. hsdp2x4) | ddp | tpTxdpD (e.g. tp2xdp4)")
     ap.add_argument("--reshard-after-forward", action="store_true", help="drop published weights after forward")
     ap.add_argument("--ns", choices=("gram", "direct"), default="gram")
     ap.add_argument("--no-e2e", action="store_true")
@@ -70,6 +70,8 @@ def parse_args():
                     help="pull each dedicated Linear weight inside its first forward GEMM (peer data plane only)")
     ap.add_argument("--attention", choices=("cudnn", "flash"), default="cudnn",
                     help="SDPA backend preference of this package's model (the reference arm uses Hugging Face's default)")
+    ap.add_argument("--clip-norm", type=float, default=0.0,
+                    help="global gradient-norm clip applied after backward (this package's arm, Muon only; 0 = off)")
     ap.add_argument("--plain-model-ops", action="store_true",
                     help="plain PyTorch SwiGLU / rotary embedding / cross-entropy instead of this package's fused kernels")
     return ap.parse_args()
@@ -164,6 +166,15 @@ def make_mesh(args, world):
     from torch.distributed.device_mesh import init_device_mesh
 
     par = args.parallelism
+    args.data_ranks, args.data_rank = world, None
+    if par.startswith("tp"):
+        # "tp2xdp4": tensor parallel inside groups of 2 neighbouring ranks, dedicated ownership + FSDP2 over 4
+        t, d = (int(x) for x in par[2:].split("xdp"))
+        assert t * d == world, f"{par} needs {t * d} ranks, got {world}"
+        mesh2 = init_device_mesh("cuda", (d, t), mesh_dim_names=("dp", "tp"))
+        args.tp_mesh = mesh2["tp"]
+        args.data_ranks, args.data_rank = d, mesh2["dp"].get_local_rank()
+        return mesh2["dp"], mesh2["dp"], None
     if par.startswith("hsdp"):
         r, s = (int(x) for x in par[4:].split("x"))
         assert r * s == world, f"{par} needs {r * s} ranks, got {world}"
@@ -202,6 +213,16 @@ def build_ours(args, dims, rank, world, device):
     mesh_all, shard_mesh, rep_mesh = make_mesh(args, world)
     mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.bfloat16)
     fsdp_mesh = mesh_all
+    if getattr(args, "tp_mesh", None) is not None:
+        from torch.distributed.tensor.parallel import ColwiseParallel, RowwiseParallel, parallelize_module
+
+        plan = {
+            "self_attn.q_proj": ColwiseParallel(), "self_attn.k_proj": ColwiseParallel(),
+            "self_attn.v_proj": ColwiseParallel(), "self_attn.o_proj": RowwiseParallel(),
+            "mlp.gate_proj": ColwiseParallel(), "mlp.up_proj": ColwiseParallel(), "mlp.down_proj": RowwiseParallel(),
+        }
+        for layer in model.layers:
+            parallelize_module(layer, args.tp_mesh, plan)
     if args.act_ckpt:
         from torch.distributed.algorithms._checkpoint.checkpoint_wrapper import checkpoint_wrapper
 
@@ -232,9 +253,13 @@ def build_ours(args, dims, rank, world, device):
         fully_shard(model, mesh=fsdp_mesh, mp_policy=mp)
         opt = torch.optim.AdamW(model.parameters(), lr=1e-3, weight_decay=0.01, fused=True)
 
+    clip = float(args.clip_norm)
+
     def fwd_bwd(b):
         loss = model(b[:, :-1], labels=b[:, 1:])
         loss.backward()
+        if clip > 0 and args.optimizer == "muon":
+            dmuon.clip_grad_norm_(opt, clip)
         return loss
 
     def launches():
@@ -354,7 +379,10 @@ def run(args):
     fwd_bwd, opt, launches = build(args, dims, rank, world, device)
     mb, seq, vocab = dims["mb"], dims["seq"], dims["vocab_size"]
 
-    gen = torch.Generator().manual_seed(1234 + rank)
+    # ranks of one tensor-parallel group see the same batch
+    data_rank = rank if getattr(args, "data_rank", None) is None else args.data_rank
+    data_ranks = getattr(args, "data_ranks", world)
+    gen = torch.Generator().manual_seed(1234 + data_rank)
     n_batches = 4
     if args.model == "pi0":
         host = [tuple(t.pin_memory() for t in pi0_host_batch(dims, mb, gen)) for _ in range(n_batches)]
@@ -417,7 +445,7 @@ def run(args):
     step_ms, opt_ms, e2e_max = (float(x) for x in t.tolist())
     peak = torch.tensor([torch.cuda.max_memory_allocated() / 2**30], device=device)
     dist.all_reduce(peak, op=dist.ReduceOp.MAX)
-    tokens = mb * seq * world
+    tokens = mb * seq * data_ranks
     if rank == 0:
         out = {
             "metric": "train_step_ms",
@@ -443,7 +471,7 @@ def run(args):
             "config": {
                 "model": args.model,
                 "optimizer": args.optimizer,
-                "global_batch": mb * world,
+                "global_batch": mb * data_ranks,
                 "micro_batch_per_gpu": mb,
                 "seq_len": seq,
                 "parallelism": (args.parallelism if args.parallelism != "fsdp" else f"fsdp{world}")

@@ -147,18 +147,18 @@ class Attention(nn.Module):
     def forward(self, x: torch.Tensor, rope: RopeTables) -> torch.Tensor:
         b, s, _ = x.shape
         q, k = self.q_proj(x), self.k_proj(x)
-        v = self.v_proj(x).view(b, s, self.n_kv, self.hd).transpose(1, 2)
+        v = self.v_proj(x).view(b, s, -1, self.hd).transpose(1, 2)   # -1: local heads under tensor parallelism
         if FUSED_OPS and q.is_cuda:
             # rotated in place, in the [b, s, h, d] layout the projections wrote
             q, k = model_ops.rope_qk_(q, k, rope.cos, rope.sin, self.hd)
-            q = q.view(b, s, self.n_heads, self.hd).transpose(1, 2)
-            k = k.view(b, s, self.n_kv, self.hd).transpose(1, 2)
+            q = q.view(b, s, -1, self.hd).transpose(1, 2)
+            k = k.view(b, s, -1, self.hd).transpose(1, 2)
         else:
             cos, sin = rope.as_dtype(q.dtype)
-            q = apply_rope(q.view(b, s, self.n_heads, self.hd).transpose(1, 2), cos, sin)
-            k = apply_rope(k.view(b, s, self.n_kv, self.hd).transpose(1, 2), cos, sin)
+            q = apply_rope(q.view(b, s, -1, self.hd).transpose(1, 2), cos, sin)
+            k = apply_rope(k.view(b, s, -1, self.hd).transpose(1, 2), cos, sin)
         o = causal_attention(q, k, v, self.n_kv != self.n_heads)
-        return self.o_proj(o.transpose(1, 2).reshape(b, s, self.n_heads * self.hd))
+        return self.o_proj(o.transpose(1, 2).reshape(b, s, -1))
 
 
 class MLP(nn.Module):

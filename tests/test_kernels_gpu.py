@@ -313,6 +313,7 @@ def test_newton_schulz_graph_replay_matches_eager(monkeypatch):
     mats = [torch.randn(384, 1024, device=dev) for _ in range(4)]
     monkeypatch.setenv("DMUON_NS_CUDA_GRAPH", "0")
     eager = [ns.local(m, 5).clone() for m in mats]
+    again = [ns.local(m, 5).clone() for m in mats]
     monkeypatch.setenv("DMUON_NS_CUDA_GRAPH", "1")
     ns_graph.cache().clear()
     base = ns_graph.cache().stats()
@@ -323,7 +324,9 @@ def test_newton_schulz_graph_replay_matches_eager(monkeypatch):
     # The Frobenius norm is accumulated with atomics, so two runs of one input differ
     # in the last bit of the scale and the fp16 iteration amplifies that to a few
     # 1e-3; a replay that used a stale input or output would be off by about 1.4.
-    for a, b in zip(got, eager):
+    # So the yardstick is the spread of two eager runs.
+    for a, b, c in zip(got, eager, again):
         rel = ((a - b).norm() / b.norm()).item()
-        assert rel < 2e-2, rel
+        spread = ((c - b).norm() / b.norm()).item()
+        assert rel < 2e-2 and rel <= 10 * spread + 1e-5, (rel, spread)
     assert dmuon.get_backend_status()["cuda_graph_replay"] is True

@@ -137,3 +137,62 @@ def test_tp_muon_matches_single_process(mode):
         assert (sd[n].float() - p).abs().max().item() < 2e-4, n
     # six TP matrices, every one orthogonalised on exactly one rank
     assert sum(r[2] for r in res) == 6
+
+
+def _llama_body(rank, world, steps):
+    import torch.distributed as dist
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+    from torch.distributed.tensor.parallel import ColwiseParallel, RowwiseParallel, parallelize_module
+
+    import dmuon_b200 as dmuon
+    from dmuon_b200.models.llama import LlamaConfig, LlamaModel
+
+    cfg = LlamaConfig.tiny(n_layers=2, loss_chunk=0)
+    torch.manual_seed(0)
+    model = LlamaModel(cfg)
+    ids = torch.randint(0, cfg.vocab_size, (4, 33), generator=torch.Generator().manual_seed(9))
+    if world == 1:
+        mesh = init_device_mesh("cpu", (1,), mesh_dim_names=("dp",))
+        dp_rank, dp = 0, 1
+    else:
+        mesh2 = init_device_mesh("cpu", (2, 2), mesh_dim_names=("dp", "tp"))
+        plan = {
+            "self_attn.q_proj": ColwiseParallel(), "self_attn.k_proj": ColwiseParallel(),
+            "self_attn.v_proj": ColwiseParallel(), "self_attn.o_proj": RowwiseParallel(),
+            "mlp.gate_proj": ColwiseParallel(), "mlp.up_proj": ColwiseParallel(), "mlp.down_proj": RowwiseParallel(),
+        }
+        for layer in model.layers:
+            parallelize_module(layer, mesh2["tp"], plan)
+        mesh = mesh2["dp"]
+        dp_rank, dp = mesh.get_local_rank(), 2
+    dmuon.dedicate_params(model, mesh, lambda n, p: "proj" in n and p.ndim == 2, reshard_after_forward=False)
+    for layer in model.layers:
+        fully_shard(layer, mesh=mesh)
+    fully_shard(model, mesh=mesh)
+    opt = dmuon.Muon(model, lr=0.02, adamw_lr=1e-3, weight_decay=0.1, first_step_progress_log=False)
+    per = 4 // dp
+    losses = []
+    for _ in range(steps):
+        b = ids[dp_rank * per : (dp_rank + 1) * per]
+        opt.zero_grad()
+        loss = model(b[:, :-1], labels=b[:, 1:])
+        loss.backward()
+        opt.step()
+        lt = loss.detach().clone()
+        dist.all_reduce(lt)
+        losses.append(lt.item() / world)
+    sd = dmuon.get_model_state_dict(model, rank0_only=False)
+    return losses, {k: v for k, v in sd.items() if "layers.1" in k}
+
+
+def test_llama_decoder_under_tensor_parallelism_matches_single_rank():
+    """The package's own decoder (heads split over the TP group) trained on a
+    DP2 x TP2 mesh follows the single-rank trajectory."""
+    steps = 3
+    ref_losses, ref_sd = run_ranks(_llama_body, 1, args=(steps,))[0]
+    losses, sd = run_ranks(_llama_body, 4, args=(steps,))[0]
+    for a, b in zip(losses, ref_losses):
+        assert abs(a - b) < 2e-4 * max(1.0, abs(b)), (losses, ref_losses)
+    for n, p in ref_sd.items():
+        assert (sd[n].float() - p.float()).abs().max().item() < 5e-4, n

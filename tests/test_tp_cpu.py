@@ -196,3 +196,58 @@ def test_llama_decoder_under_tensor_parallelism_matches_single_rank():
         assert abs(a - b) < 2e-4 * max(1.0, abs(b)), (losses, ref_losses)
     for n, p in ref_sd.items():
         assert (sd[n].float() - p.float()).abs().max().item() < 5e-4, n
+
+
+def _body_3d(rank, world, steps):
+    import torch.distributed as dist
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+    from torch.distributed.tensor.parallel import ColwiseParallel, RowwiseParallel, parallelize_module
+
+    import dmuon_b200 as dmuon
+
+    mesh = init_device_mesh("cpu", (2, 2, 2), mesh_dim_names=("replicate", "shard", "tp"))
+    torch.manual_seed(0)
+    model = Net()
+    for blk in model.layers:
+        parallelize_module(blk, mesh["tp"], {"up_proj": ColwiseParallel(), "down_proj": RowwiseParallel()})
+    owners = dmuon.dedicate_params(model, mesh["shard"], _pred, reshard_after_forward=False,
+                                   replicate_mesh=mesh["replicate"])
+    hsdp = mesh["replicate", "shard"]
+    for blk in model.layers:
+        fully_shard(blk, mesh=hsdp)
+    fully_shard(model, mesh=hsdp)
+    opt = dmuon.Muon(model, lr=LR, momentum=MU, weight_decay=WD, adamw_lr=ALR)
+    dp_rank = mesh["replicate"].get_local_rank() * 2 + mesh["shard"].get_local_rank()
+    losses = []
+    for s in range(steps):
+        x, y = _data(s)
+        x, y = x[dp_rank * 2 : dp_rank * 2 + 2], y[dp_rank * 2 : dp_rank * 2 + 2]
+        opt.zero_grad()
+        loss = (model(x) - y).pow(2).mean()
+        loss.backward()
+        opt.step()
+        lt = loss.detach().clone()
+        dist.all_reduce(lt)
+        losses.append((lt / world).item())
+    sd = dmuon.get_model_state_dict(model, rank0_only=False)
+    coords = sorted({tuple(v) if isinstance(v, tuple) else (v,) for v in owners.values()})
+    return losses, sd, coords
+
+
+def test_three_dimensional_mesh_replicate_shard_tp_matches_single_process():
+    """R2 x S2 x T2 on eight gloo ranks: two-stage reduce to a 2-D owner
+    coordinate, TP gather/scatter inside each owner's TP group, replicate
+    publish -- same trajectory as one process."""
+    steps = 3
+    ref_losses, ref_params = _oracle(steps)
+    res = run_ranks(_body_3d, 8, args=(steps,), timeout=480)
+    losses, sd, coords = res[0]
+    assert all(len(c) == 2 for c in coords) and len(coords) > 1      # 2-D owner coordinates, more than one owner
+    for a, b in zip(losses, ref_losses):
+        assert abs(a - b) < 1e-4 * max(1.0, abs(b)), (losses, ref_losses)
+    for n, p in ref_params.items():
+        assert (sd[n].float() - p).abs().max().item() < 2e-4, n
+    for r in range(1, 8):
+        for n in sd:
+            assert torch.equal(sd[n], res[r][1][n]), (r, n)

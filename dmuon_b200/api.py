@@ -112,7 +112,14 @@ class _ModelIndex:
                 common.append(col[0])
             else:
                 break
-        return self.model.get_submodule(".".join(common)) if common else self.model
+        # a pure container (ModuleList, ModuleDict, ...) is never called, so hooks on it
+        # would never fire: climb to the first ancestor that has a forward of its own
+        while common:
+            mod = self.model.get_submodule(".".join(common))
+            if type(mod).forward is not nn.Module.forward:
+                return mod
+            common.pop()
+        return self.model
 
 
 def _resolve_hook_module(index: _ModelIndex, p, fqn, predicate, resolver, strict) -> nn.Module:

@@ -101,6 +101,30 @@ def _wrap_first_grad_tensor(node_cls, state, obj):
     return obj, False
 
 
+def _wrap_every_grad_tensor(node_cls, state, obj):
+    """Route every grad-requiring top-level tensor of a module output through
+    its own ``node_cls`` node: whichever of them the loss is built from (the
+    logits, or a loss the module computed itself), backward passes the node
+    before it reaches the module's parameters."""
+    def wrap(it):
+        if isinstance(it, torch.Tensor) and it.requires_grad:
+            return node_cls.apply(state, it)[0]
+        return it
+
+    if isinstance(obj, torch.Tensor):
+        return wrap(obj)
+    if isinstance(obj, list):
+        return [wrap(it) for it in obj]
+    if isinstance(obj, tuple):
+        items = [wrap(it) for it in obj]
+        return type(obj)(*items) if hasattr(obj, "_fields") else tuple(items)
+    if isinstance(obj, dict):
+        for k in list(obj.keys()):
+            obj[k] = wrap(obj[k])           # in place: attribute access on ModelOutput-like dicts keeps working
+        return obj
+    return obj
+
+
 class DedicatedState:
     def __init__(self, module: nn.Module, group, comm_ctx: DedicatedCommContext):
         self.module = module
@@ -158,7 +182,7 @@ class DedicatedState:
         if not recompute:
             group._record_post_forward()
         if torch.is_grad_enabled() and not recompute:
-            output, _ = _wrap_first_grad_tensor(_PreBackwardNode, self, output)
+            output = _wrap_every_grad_tensor(_PreBackwardNode, self, output)
         pol = group.params[0] if group.params else None
         if pol is not None and pol._output_dtype is not None:
             output = _map_tensors(_cast_floating(pol._output_dtype), output)

@@ -1,0 +1,166 @@
+"""Behavioural details a drop-in replacement has to keep (2 gloo ranks): tied
+dedicated weights, dict-like model outputs, parameters that receive no
+gradient, the constructor guard, ``zero_grad`` bookkeeping, activation casts."""
+import pytest
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from dist_utils import run_ranks
+
+
+class Out(dict):
+    """Minimal stand-in for a Hugging Face ``ModelOutput``: a dict with attribute access."""
+
+    def __getattr__(self, k):
+        try:
+            return self[k]
+        except KeyError as exc:
+            raise AttributeError(k) from exc
+
+
+class Block(nn.Module):
+    def __init__(self, d):
+        super().__init__()
+        self.in_proj = nn.Linear(d, d, bias=False)
+        self.out_proj = nn.Linear(d, d, bias=False)
+        self.unused_proj = nn.Linear(d, d, bias=False)       # never called: no gradient, ever
+
+    def forward(self, x):
+        return x + self.out_proj(torch.tanh(self.in_proj(x)))
+
+
+class TiedNet(nn.Module):
+    def __init__(self, d=16, vocab=32):
+        super().__init__()
+        self.embed = nn.Embedding(vocab, d)
+        self.blocks = nn.ModuleList(Block(d) for _ in range(2))
+        self.blocks[1].in_proj.weight = self.blocks[0].in_proj.weight      # one matrix, two call sites
+        self.norm = nn.LayerNorm(d)
+        self.head = nn.Linear(d, vocab, bias=False)
+
+    def forward(self, ids, labels=None):
+        x = self.embed(ids)
+        for b in self.blocks:
+            x = b(x)
+        logits = self.head(self.norm(x))
+        out = Out(logits=logits)
+        if labels is not None:
+            out["loss"] = F.cross_entropy(logits.flatten(0, 1), labels.flatten())
+        return out
+
+
+def _pred(n, p):
+    return "proj" in n and p.ndim == 2
+
+
+def _single_process_reference(steps, ids):
+    import math
+
+    from dmuon_b200.optim.newton_schulz import gram_newton_schulz
+
+    torch.manual_seed(0)
+    model = TiedNet()
+    params = dict(model.named_parameters())             # tied weight appears once
+    mom = {}
+    losses = []
+    for _ in range(steps):
+        model.zero_grad()
+        loss = model(ids, labels=ids).loss
+        loss.backward()
+        losses.append(loss.item())
+        with torch.no_grad():
+            for n, p in params.items():
+                if not _pred(n, p) or p.grad is None:
+                    continue
+                buf = mom.setdefault(n, torch.zeros_like(p))
+                buf.mul_(0.95).add_(p.grad)
+                o = gram_newton_schulz(p.grad.add(buf, alpha=0.95))
+                p.add_(o, alpha=-0.05 * 0.2 * math.sqrt(max(p.shape)))
+    return losses, {n: p.detach().clone() for n, p in params.items() if _pred(n, p)}
+
+
+def _body(rank, world, steps):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+
+    torch.manual_seed(0)
+    model = TiedNet()
+    mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("dp",))
+    # the guard: non-dedicated trainable parameters must be managed by FSDP2 or replicate
+    dmuon.dedicate_params(model, mesh, _pred, reshard_after_forward=True)
+    try:
+        dmuon.Muon(model, first_step_progress_log=False)
+        guard = False
+    except RuntimeError:
+        guard = True
+    fully_shard(model, mesh=mesh)
+    # adamw_lr 0: only the Muon matrices move, which is what the reference below reproduces
+    opt = dmuon.Muon(model, lr=0.05, adamw_lr=0.0, adamw_weight_decay=0.0, first_step_progress_log=False)
+    dps = {p.fqn: p for p in dmuon.get_dedicated_params(model)}
+    tied = dps["blocks.0.in_proj.weight"]
+    ids = torch.randint(0, 32, (4, 8), generator=torch.Generator().manual_seed(7))
+    losses, attr_ok = [], True
+    for _ in range(steps):
+        opt.zero_grad()
+        out = model(ids, labels=ids)                       # same batch on both ranks: the mean equals one rank's gradient
+        attr_ok = attr_ok and isinstance(out, Out) and out.loss is out["loss"]
+        out.loss.backward()
+        opt.step()
+        losses.append(out.loss.item())
+    # a parameter that never got a gradient: no momentum, untouched weights, no crash
+    unused = dps["blocks.0.unused_proj.weight"]
+    unused_state = "momentum_buffer" in opt.state.get(id(unused), {})
+    opt.zero_grad()
+    cleared = all(p._reduced_grad is None and p._accumulated_grad is None for p in dps.values())
+    sd = dmuon.get_model_state_dict(model, rank0_only=False)
+    return (guard, sorted(tied.alias_fqns), losses, attr_ok, unused_state, cleared,
+            {k: v for k, v in sd.items() if "proj" in k}, sorted(sd))
+
+
+def test_tied_weights_dict_outputs_unused_parameters_and_guard():
+    steps = 4
+    ids = torch.randint(0, 32, (4, 8), generator=torch.Generator().manual_seed(7))
+    ref_losses, ref_params = _single_process_reference(steps, ids)
+    for guard, aliases, losses, attr_ok, unused_state, cleared, sd, names in run_ranks(_body, 2, args=(steps,)):
+        assert guard and attr_ok and cleared and not unused_state
+        assert aliases == ["blocks.0.in_proj.weight", "blocks.1.in_proj.weight"]
+        assert "blocks.1.in_proj.weight" in names              # state dict lists every alias, like nn.Module.state_dict
+        for a, b in zip(losses, ref_losses):
+            assert abs(a - b) < 1e-4 * max(1.0, abs(b)), (losses, ref_losses)
+        for n, p in ref_params.items():
+            assert (sd[n] - p).abs().max().item() < 2e-4, n
+        assert torch.equal(sd["blocks.0.in_proj.weight"], sd["blocks.1.in_proj.weight"])
+
+
+def _cast_body(rank, world):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(8, 8, bias=False), nn.Linear(8, 8, bias=False))
+    mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("dp",))
+    dmuon.dedicate_params(
+        model, mesh, lambda n, p: p.ndim == 2, hook_boundary_predicate=lambda m: isinstance(m, nn.Linear),
+        reshard_after_forward=False,
+        param_policy={"defaults": {"param_dtype": "bf16", "output_dtype": "fp32", "cast_forward_inputs": True}},
+    )
+    fully_shard(model, mesh=mesh)
+    seen = []
+    model[1].register_forward_pre_hook(lambda m, a: seen.append(a[0].dtype))
+    y = model(torch.randn(2, 8))
+    live = model[0].weight.dtype
+    masters = {p._owned_data.dtype for p in dmuon.get_owned_params(model)}
+    return str(y.dtype), [str(d) for d in seen], str(live), sorted(str(m) for m in masters)
+
+
+def test_activation_casts_at_the_hook_boundary():
+    for y_dtype, seen, live, masters in run_ranks(_cast_body, 2):
+        assert y_dtype == "torch.float32"                  # output_dtype
+        assert live == "torch.bfloat16"                    # param_dtype of the live weights
+        assert masters in (["torch.float32"], [])          # fp32 masters on the owner
+        assert seen and seen[0] in ("torch.float32", "torch.bfloat16")

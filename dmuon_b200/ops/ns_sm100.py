@@ -7,15 +7,23 @@ the whole batch, so small Gram dimensions (1024, 256) still fill 148 SMs.
 Data flow for a batch of ``L`` matrices ``m0 x n0`` (natural orientation, no
 transposed copy is ever made):
 
-    prologue      mom = mu*mom + g ; u = g + mu*mom ; X = bf16(u) ; sumsq += u^2
+    prologue      mom = mu*mom + g ; u = g + mu*mom ; sumsq += u^2
+                  (with the peer data plane the same kernel first sums g over
+                  all ranks' gradient arenas: reduce-to-owner costs no extra pass)
     scales        s = 1/(||u||_F + eps), s^2
-    gram          R = s^2 X X^T   (m0 <= n0)   or   s^2 X^T X   (m0 > n0)
+    operand       Gram form (default): X = fp16(K s u), K a power of two near
+                  sqrt(min(m0, n0)) that keeps entries clear of fp16 subnormals;
+                  the products carry 1/K^2 and 1/K in their alpha.
+                  bf16 operands (compute_dtype=bf16): X = bf16(u) written by the
+                  prologue itself, s and s^2 applied per matrix in the epilogues.
+    gram          R = X X^T   (m0 <= n0)   or   X^T X   (m0 > n0)
     per step      P = c R R + b R + a I ;  Q = P Q ;  R = (R P) P      symmetric
-    restart       X = s Q X  (or s X Q) ;  R = X X^T
-    final         W = (1 - lr wd) W - lr * scale * s * Q X   written straight
-                  into the fp32 master weights (and a bf16 publish copy)
+    restart       X = Q X  (or X Q) ;  R = X X^T
+    final         W = (1 - lr wd) W - lr * scale * Q X   written straight into
+                  the fp32 master weights (and a bf16 publish copy)
 
-Symmetric products compute only the tiles that touch the lower triangle.
+Symmetric products compute only the tiles that touch the lower triangle (the
+CTA-pair kernel, 256 x 256 tiles, whenever the shape fills it).
 Replaces the reference's per-matrix Python loop around SYRK / cuBLAS calls and
 its CUDA-graph cache (dmuon/optim/muon.py:1582-1747,
 dmuon/optim/newton_schulz.py:333-448, dmuon/optim/ns_graph.py:61-128).

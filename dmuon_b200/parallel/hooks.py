@@ -226,7 +226,9 @@ def _root_post_backward(ctx: DedicatedCommContext) -> None:
     """Runs once when the whole backward graph has been executed."""
     for st in ctx.all_states:
         if st._forward_ran and not st._post_backward_ran:
-            has_grad = any(p.local_grad() is not None for p in st.group.params)
+            has_grad = any(
+                p.local_grad() is not None or getattr(p, "_grad_in_arena", False) for p in st.group.params
+            )
             if has_grad or st.group._is_unsharded:
                 st._post_backward_ran = False
                 st._post_backward()

@@ -110,6 +110,56 @@ def _fused_linear_forward(self, x):
     return F.linear(x, w, self.bias)
 
 
+def direct_wgrad_requested() -> bool:
+    return os.environ.get("DMUON_DIRECT_WGRAD", "1").strip().lower() in ("1", "true", "yes", "on")
+
+
+class _LinearGradToArena(torch.autograd.Function):
+    """``F.linear`` whose weight gradient is written by the backward GEMM
+    straight into this rank's slot of the gradient arena (the memory the owner
+    reads through its peer mapping), instead of into a fresh tensor that is
+    packed into the arena afterwards.  Later micro-batches accumulate in place."""
+
+    @staticmethod
+    def forward(ctx, x, w, b, rt, p):
+        ctx.save_for_backward(x, w)
+        ctx.rt, ctx.p, ctx.has_bias = rt, p, b is not None
+        return torch.nn.functional.linear(x, w, b)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        rt, p = ctx.rt, ctx.p
+        dx = dw = db = None
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if ctx.needs_input_grad[0]:
+            dx = (dy2 @ w).view(x.shape)
+        if ctx.needs_input_grad[1]:
+            x2 = x.reshape(-1, x.shape[-1])
+            slot = p._grad_view
+            if slot.dtype == dy2.dtype == x2.dtype:
+                rt.before_pack()                    # owners are done with last step's slots (once per step)
+                if p._peer_grad_pending:
+                    slot.addmm_(dy2.t(), x2)
+                else:
+                    torch.mm(dy2.t(), x2, out=slot)
+                    p._peer_grad_pending = True
+                p._grad_in_arena = True
+            else:
+                dw = dy2.t() @ x2
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.sum(dim=0)
+        return dx, dw, db, None, None
+
+
+def _direct_wgrad_linear_forward(self, x):
+    rt, p = self._dmuon_direct
+    w = self.weight
+    if torch.is_grad_enabled() and w.requires_grad and w.numel() == p.numel and x.dtype == w.dtype:
+        return _LinearGradToArena.apply(x, w, self.bias, rt, p)
+    return torch.nn.functional.linear(x, w, self.bias)
+
+
 class PeerRuntime:
     def __init__(self, ctx, dp_group, groups: list["PeerParamGroup"], fused_forward: Optional[bool] = None):
         import torch.distributed._symmetric_memory as symm_mem
@@ -171,6 +221,9 @@ class PeerRuntime:
         self.fused_forward = fused_forward_requested() if fused_forward is None else bool(fused_forward)
         if self.fused_forward:
             self._install_fused_linears()
+        self.direct_wgrad = direct_wgrad_requested() and not self.fused_forward
+        if self.direct_wgrad:
+            self._install_direct_wgrad_linears()
         dist.barrier(group=dp_group)
         self.publish_owned()
 
@@ -196,6 +249,26 @@ class PeerRuntime:
                 p._fused_epoch = -1
                 mod._dmuon_fused = (self, p)
                 mod.forward = types.MethodType(_fused_linear_forward, mod)
+
+    def _install_direct_wgrad_linears(self) -> None:
+        """Plain ``nn.Linear`` modules whose weight is a dedicated matrix get a
+        forward whose backward writes the weight gradient into the arena slot.
+        Shared weights, custom modules and direct ``.weight`` use keep the
+        ordinary autograd path (their gradients are packed afterwards)."""
+        import types
+
+        import torch.nn as nn
+
+        for g in self.groups:
+            for p in g.bcast_params:
+                p._grad_in_arena = False
+                if len(p.alias_sites) != 1 or len(p._orig_size) != 2:
+                    continue
+                mod, attr = p.alias_sites[0]
+                if type(mod) is not nn.Linear or attr != "weight":
+                    continue
+                mod._dmuon_direct = (self, p)
+                mod.forward = types.MethodType(_direct_wgrad_linear_forward, mod)
 
     def fused_pull_args(self, p: DedicatedParam):
         esz = self.pub.element_size()
@@ -432,10 +505,14 @@ class PeerParamGroup(DedicatedParamGroup):
 
     def reduce_grads(self) -> None:
         with_grad = [(p, p.local_grad()) for p in self.bcast_params]
+        # gradients the backward GEMMs already wrote into the arena
+        direct = [p for p, g in with_grad if getattr(p, "_grad_in_arena", False)]
         with_grad = [(p, g) for p, g in with_grad if g is not None]
-        if not with_grad:
+        if not with_grad and not direct:
             return
         rt = self.runtime
+        for p in direct:
+            p._grad_in_arena = False
         with torch.no_grad():
             rt.before_pack()
             dsts = [p._grad_view for p, _ in with_grad]
@@ -456,7 +533,8 @@ class PeerParamGroup(DedicatedParamGroup):
             # micro-batch repeats this and overwrites the result with the larger sum.
             self._pack_count += 1
             rt.signal_group_packed(self, self._pack_count)
-            owned = [p for p, _ in with_grad if p.is_owner]
+            seen = {id(p) for p, _ in with_grad}
+            owned = [p for p, _ in with_grad if p.is_owner] + [p for p in direct if p.is_owner and id(p) not in seen]
             if owned:
                 self._reduce_ticket = rt.launch_group_reduce(self, owned, self._pack_count)
                 self._reduce_owned = owned

@@ -177,7 +177,9 @@ def _train_body(rank, world, backend, steps):
     if used_peer:
         model._dedicated_comm_ctx.peer_runtime.check()
     sd = dmuon.get_model_state_dict(model, rank0_only=False)
-    return losses, {k: v for k, v in sd.items() if "proj" in k}, used_peer
+    # weight gradients of plain Linear layers go straight into the arena unless the fused publish owns the forward
+    direct = sum(1 for m in model.modules() if hasattr(m, "_dmuon_direct"))
+    return losses, {k: v for k, v in sd.items() if "proj" in k}, used_peer, direct
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
@@ -188,6 +190,7 @@ def test_peer_data_plane_matches_nccl():
     got = run_ranks(_train_body, world, args=("peer", steps), backend="nccl", timeout=600)
     alt = run_ranks(_train_body, world, args=("peer-optimizer-reduce", steps), backend="nccl", timeout=600)
     assert not ref[0][2] and got[0][2] and alt[0][2]
+    assert ref[0][3] == 0 and got[0][3] == 21 and alt[0][3] == 21      # 3 layers x 7 projections
     for a, b, c in zip(got[0][0], ref[0][0], alt[0][0]):
         assert abs(a - b) < 2e-2 * max(1.0, abs(b)), (got[0][0], ref[0][0])
         assert abs(c - b) < 2e-2 * max(1.0, abs(b)), (alt[0][0], ref[0][0])

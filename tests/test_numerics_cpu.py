@@ -127,3 +127,21 @@ def test_graph_cache_is_transparent_on_cpu_and_counts_calls(monkeypatch):
     assert ns_graph.enabled() is False
     monkeypatch.setenv("DMUON_NS_CUDA_GRAPH", "1")
     assert ns_graph.enabled() is True
+
+
+def test_precision_study_runs_and_metrics_behave():
+    import importlib.util
+    import os
+
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "benchmarks", "ns_precision.py")
+    spec = importlib.util.spec_from_file_location("ns_precision", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    G, nuclear = mod.make_matrix("uniform", 16, 48, seed=1)
+    assert abs(nuclear - float(torch.linalg.svdvals(G.double()).sum())) < 1e-3 * nuclear     # the construction's spectrum
+    Uo, _, Vh = torch.linalg.svd(G.double(), full_matrices=False)
+    exact = mod.metrics((Uo @ Vh).float(), G, nuclear)                                      # the true polar factor
+    assert exact["orth_err"] < 1e-5 and exact["sym_err"] < 1e-5 and abs(exact["dual_gap"]) < 1e-5
+    rows = mod.run([(16, 48)], ["polar"], ["flat", "spike"], torch.device("cpu"))
+    assert [r["variant"] for r in rows] == ["fp32", "fp32"] and all(r["vs_fp32"] == 0.0 for r in rows)
+    assert all(r["orth_err"] < 0.35 and r["sym_err"] < 1e-3 and r["psd_violation"] < 1e-3 for r in rows)

@@ -87,14 +87,27 @@ def status_buffer(device: torch.device) -> torch.Tensor:
     return buf
 
 
+_STATUS_NAMES = {
+    1: "TMA producer waited for a free pipeline stage",
+    2: "MMA issuer waited for operands or a free accumulator",
+    3: "epilogue waited for an accumulator",
+    4: "wait on a peer / ready flag ran out (a rank did not signal in time)",
+    5: "bad argument",
+}
+
+
+def describe_status(code: int) -> str:
+    """What a non-zero status word written by one of the kernels means."""
+    return _STATUS_NAMES.get(int(code), f"unknown status {int(code)}")
+
+
 def check_status(device: torch.device | None = None) -> None:
     """Synchronising read of the status word; raises if any kernel gave up."""
     device = device or torch.device("cuda", torch.cuda.current_device())
     code = int(status_buffer(device)[0].item())
     if code != 0:
         status_buffer(device).zero_()
-        names = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue", 4: "peer/ready flag", 5: "bad argument"}
-        raise KernelTimeout(f"dmuon_b200 kernel wait ran out (code {code}: {names.get(code, '?')})")
+        raise KernelTimeout(f"dmuon_b200 kernel wait ran out (code {code}: {describe_status(code)})")
 
 
 def symmetric_tiles(m: int, bn: int, bm: int = BM) -> list[tuple[int, int, int]]:

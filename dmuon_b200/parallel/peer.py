@@ -40,6 +40,8 @@ ALIGN = 64          # elements; keeps every slot 128-byte aligned for bf16
 #: CTAs per tensor of the in-backward reduce: enough loads in flight for NVLink
 #: (about 28 KB per CTA) without taking many SMs from the backward GEMMs
 REDUCE_BLOCKS_PER_TENSOR = 24
+#: value of the guard words around the arenas in canary mode (exact in bf16, fp16 and fp32)
+CANARY_VALUE = -1.5
 
 
 def peer_backend_requested() -> str:
@@ -175,14 +177,20 @@ class PeerRuntime:
         params = [p for g in groups for p in g.bcast_params]
         self.param_dtype = params[0]._param_dtype
         self.grad_dtype = params[0]._grad_dtype or params[0]._param_dtype
-        off = 0
+        # Debug aid (DMUON_DEBUG_CANARY=1): a guard band of known words before the first
+        # and after the last slot of both arenas; ``check()`` verifies them, which catches
+        # a kernel (local or a peer's) that writes outside the slots it was given.
+        self.canary = os.environ.get("DMUON_DEBUG_CANARY", "0").strip().lower() in ("1", "true", "yes", "on")
+        self.guard = 4 * ALIGN if self.canary else 0
+        off = self.guard
         # owner-major layout: one contiguous span per owner, groups in forward order inside it
         for s in range(self.world):
             for g in groups:
                 for p in g._pub_by_shard.get(s, ()):
                     p._arena_offset = off
                     off += (p.numel + ALIGN - 1) // ALIGN * ALIGN
-        self.total = max(off, ALIGN)
+        self.payload_end = off
+        self.total = max(off, ALIGN) + self.guard
         self.pub = symm_mem.empty(self.total, dtype=self.param_dtype, device=self.device)
         self.grad = symm_mem.empty(self.total, dtype=self.grad_dtype, device=self.device)
         # four global epoch rows, then one "gradients packed" row per group
@@ -194,6 +202,10 @@ class PeerRuntime:
             g._group_index = i
         self.flags.zero_()
         self.grad.zero_()
+        if self.canary:
+            for arena in (self.pub, self.grad):
+                arena[: self.guard].fill_(CANARY_VALUE)
+                arena[self.payload_end :].fill_(CANARY_VALUE)
         torch.cuda.synchronize(self.device)
         name = dp_group.group_name
         self.pub_hdl = symm_mem.rendezvous(self.pub, name)
@@ -290,10 +302,16 @@ class PeerRuntime:
         P.wait_flags(self.flags, kind * MAX_PEERS, self.world, want, self.status)
 
     def check(self) -> None:
-        """Synchronising status check (raises KernelTimeout when a wait gave up)."""
+        """Synchronising status check (raises KernelTimeout when a wait gave up;
+        with ``DMUON_DEBUG_CANARY=1`` also verifies the guard bands of the arenas)."""
         from ..ops import gemm as G
 
         G.check_status(self.device)
+        if self.canary:
+            for name, arena in (("publish", self.pub), ("gradient", self.grad)):
+                lo, hi = arena[: self.guard], arena[self.payload_end :]
+                if not (bool((lo == CANARY_VALUE).all()) and bool((hi == CANARY_VALUE).all())):
+                    raise RuntimeError(f"rank {self.rank}: the guard band of the {name} arena was overwritten")
 
     # ------------------------------------------------------------------ publish side
     def before_owner_writes(self) -> None:

@@ -223,6 +223,7 @@ def _reduce_check_body(rank, world, fused=False, reduce_mode="backward"):
     import torch.distributed as dist
 
     os.environ["DMUON_PEER_REDUCE"] = reduce_mode
+    os.environ["DMUON_DEBUG_CANARY"] = "1"          # guard bands around both arenas, verified by rt.check()
     if fused:
         os.environ["DMUON_FUSED_PUBLISH"] = "1"
     from torch.distributed.device_mesh import init_device_mesh
@@ -268,6 +269,7 @@ def _reduce_check_body(rank, world, fused=False, reduce_mode="backward"):
             ref = dp._owned_data.to(torch.bfloat16) if dp.is_owner else torch.empty(dp._orig_size, dtype=torch.bfloat16, device=dev)
             dist.broadcast(ref, src=dp.owner_shard)
             assert torch.equal(dp._unsharded_param.data, ref), dp.fqn
+    assert rt.canary and rt.guard > 0
     rt.check()
     return worst
 

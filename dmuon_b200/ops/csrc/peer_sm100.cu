@@ -276,3 +276,12 @@ extern "C" int dmuon_peer_pull(const DmuonPullArgs* a, void* stream_v) {
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }
+
+// One asynchronous copy on the copy engines (no SM is involved, so transfers
+// that overlap forward / backward GEMMs take nothing from them).  Either
+// pointer may be a peer mapping of another GPU's symmetric buffer.
+extern "C" int dmuon_copy_async(void* dst, const void* src, long long nbytes, void* stream_v) {
+  if (nbytes <= 0) return 0;
+  return static_cast<int>(
+      cudaMemcpyAsync(dst, src, static_cast<size_t>(nbytes), cudaMemcpyDefault, reinterpret_cast<cudaStream_t>(stream_v)));
+}

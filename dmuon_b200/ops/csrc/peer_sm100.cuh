@@ -73,4 +73,7 @@ int dmuon_signal_peers(const DmuonSignalArgs* a, void* stream);
 int dmuon_wait_flags(const DmuonWaitArgs* a, void* stream);
 int dmuon_peer_prologue(const DmuonPeerPrologueArgs* a, void* stream);
 int dmuon_peer_pull(const DmuonPullArgs* a, void* stream);
+
+// Copy-engine transfer (cudaMemcpyAsync, cudaMemcpyDefault); dst / src may be peer mappings.
+int dmuon_copy_async(void* dst, const void* src, long long nbytes, void* stream);
 }

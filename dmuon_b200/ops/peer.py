@@ -60,7 +60,15 @@ def _lib():
         fn = getattr(lib, name)
         fn.argtypes = [ctypes.POINTER(typ), ctypes.c_void_p]
         fn.restype = ctypes.c_int
+    lib.dmuon_copy_async.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_void_p]
+    lib.dmuon_copy_async.restype = ctypes.c_int
     return lib
+
+
+def copy_async(dst_ptr: int, src_ptr: int, nbytes: int, device: torch.device) -> None:
+    """Queue one copy-engine transfer on the current stream of ``device``;
+    either address may lie in a peer's symmetric buffer."""
+    _check(_lib().dmuon_copy_async(dst_ptr, src_ptr, int(nbytes), _stream(device)), "dmuon_copy_async")
 
 
 def wait_budget_cycles() -> int:

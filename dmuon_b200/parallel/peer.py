@@ -13,6 +13,14 @@ gradient arena  each rank's local gradients.  Nothing is sent after backward:
                 1/N and applies momentum / Nesterov / cast / Frobenius norm in
                 the same pass.
 
+Bulk data crosses NVLink in one of two ways (``DMUON_PEER_COPY``).  "ce", the
+default: copy-engine transfers.  Readers pull publish spans with asynchronous
+copies, owners gather the peers' gradient slices of each layer into local
+staging buffers while backward is still running, and the fixed-order fp32 sum
+runs locally inside the Muon prologue; no SM is taken from the forward and
+backward GEMMs.  "sm": the pull and reduce kernels load through the peer
+mappings themselves (the form the fused forward GEMM builds on).
+
 Ordering uses four monotonically increasing epoch words per rank in a
 symmetric flag array (gradients ready / consumed, weights published /
 consumed).  Waits are small kernels or kernel preambles with a cycle budget;
@@ -77,7 +85,8 @@ class PeerSource:
     """What the fused prologue needs to read one batch of gradients."""
 
     def __init__(self, rt: "PeerRuntime", dparams: list[DedicatedParam]):
-        self.peer_bases = rt.grad_ptrs
+        # "ce" copy mode: the peers' slices were gathered into local staging buffers during backward
+        self.peer_bases = rt.stage_bases if rt.copy_mode == "ce" else rt.grad_ptrs
         self.offsets = [p._arena_offset for p in dparams]
         self.numels = [p.numel for p in dparams]
         self.grad_dtype = rt.grad_dtype
@@ -231,6 +240,37 @@ class PeerRuntime:
                 p._peer_grad_pending = False
         self._remote_groups = sum(1 for g in groups if any(s != self.rank for s in g._pub_by_shard))
         self.fused_forward = fused_forward_requested() if fused_forward is None else bool(fused_forward)
+        # How bulk data crosses NVLink: "ce" (default) uses copy-engine transfers -- publish pulls and a
+        # gather of the peers' gradient slices into local staging buffers, the sum then happens locally
+        # inside the Muon prologue -- so no SM is taken from the forward / backward GEMMs; "sm" uses the
+        # pull / reduce kernels that load through the peer mappings themselves.
+        self.copy_mode = os.environ.get("DMUON_PEER_COPY", "ce").strip().lower()
+        if self.copy_mode not in ("ce", "sm"):
+            raise ValueError("DMUON_PEER_COPY must be 'ce' or 'sm'")
+        if self.fused_forward:
+            self.copy_mode = "sm"       # the fused forward kernels do their own fetching
+        for g in groups:
+            g._span_by_owner = {}
+            for s_, plist in g._pub_by_shard.items():
+                lo = min(p._arena_offset for p in plist)
+                hi = max(p._arena_offset + (p.numel + ALIGN - 1) // ALIGN * ALIGN for p in plist)
+                g._span_by_owner[s_] = (lo, hi)
+        mine = [sp[self.rank] for sp in (g._span_by_owner for g in groups) if self.rank in sp]
+        self.own_lo = min((lo for lo, _ in mine), default=0)
+        self.own_hi = max((hi for _, hi in mine), default=0)
+        self.stage = None
+        self.stage_bases = list(self.grad_ptrs)
+        if self.copy_mode == "ce" and self.own_hi > self.own_lo and self.world > 1:
+            span = self.own_hi - self.own_lo
+            self.stage = torch.empty((self.world - 1) * span, dtype=self.grad_dtype, device=self.device)
+            gsz = self.grad.element_size()
+            k = 0
+            for r in range(self.world):
+                if r == self.rank:
+                    continue
+                # address of arena offset 0 in rank r's staged copy (only [own_lo, own_hi) is backed)
+                self.stage_bases[r] = self.stage.data_ptr() + (k * span - self.own_lo) * gsz
+                k += 1
         if self.fused_forward:
             self._install_fused_linears()
         self.direct_wgrad = direct_wgrad_requested() and not self.fused_forward
@@ -390,8 +430,14 @@ class PeerRuntime:
         slots = [KIND_PUB_READY * MAX_PEERS + s for s, _, _ in spans]
         live = tuple(p._unsharded_param for p in plist)
         with torch.no_grad(), torch.autograd._unsafe_preserve_version_counter(live):
-            P.peer_pull(srcs, dsts, nbytes, slots, self.flags, self.pub_epoch, self.status, self.device,
-                        blocks_per_tensor=max(4, 32 // len(srcs)))
+            if self.copy_mode == "ce":
+                # one bounded wait for the owners' "published" flags, then copy-engine transfers
+                P.wait_flags(self.flags, KIND_PUB_READY * MAX_PEERS, self.world, self.pub_epoch, self.status)
+                for src, dst, nb in zip(srcs, dsts, nbytes):
+                    P.copy_async(dst, src, nb, self.device)
+            else:
+                P.peer_pull(srcs, dsts, nbytes, slots, self.flags, self.pub_epoch, self.status, self.device,
+                            blocks_per_tensor=max(4, 32 // len(srcs)))
 
     # ------------------------------------------------------------------ gradient side
     def before_pack(self) -> None:
@@ -423,6 +469,18 @@ class PeerRuntime:
         from ..ops import peer as P
 
         lane = self.ctx.reduce_lane
+        if self.copy_mode == "ce":
+            # gather instead of reduce: bring every peer's slice of this group's owned span into the
+            # local staging buffers with copy-engine transfers; the Muon prologue sums them later
+            lo, hi = g._span_by_owner[self.rank]
+            gsz = self.grad.element_size()
+            lane.follow_current()
+            with lane.use():
+                P.wait_flags(self.flags, (4 + g._group_index) * MAX_PEERS, self.world, count, self.status)
+                for r in range(self.world):
+                    if r != self.rank:
+                        P.copy_async(self.stage_bases[r] + lo * gsz, self.grad_ptrs[r] + lo * gsz, (hi - lo) * gsz, self.device)
+            return lane.mark()
         for p in owned:
             if getattr(p, "_reduce_buf", None) is None:
                 p._reduce_buf = torch.empty(p._orig_size, dtype=torch.float32, device=self.device)
@@ -545,7 +603,7 @@ class PeerParamGroup(DedicatedParamGroup):
                 p._peer_grad_pending = True
                 p.clear_local_grad()
         self._packed_this_step = True
-        if rt.reduce_mode == "backward" and not self._no_sync:
+        if (rt.reduce_mode == "backward" or rt.copy_mode == "ce") and not self._no_sync:
             # tell every rank this group's running sum is in the arena, then (as an
             # owner) reduce it on the side lane while backward continues.  A later
             # micro-batch repeats this and overwrites the result with the larger sum.
@@ -555,7 +613,8 @@ class PeerParamGroup(DedicatedParamGroup):
             owned = [p for p, _ in with_grad if p.is_owner] + [p for p in direct if p.is_owner and id(p) not in seen]
             if owned:
                 self._reduce_ticket = rt.launch_group_reduce(self, owned, self._pack_count)
-                self._reduce_owned = owned
+                # after a copy-engine gather the sum is still to be done (inside the Muon prologue)
+                self._reduce_owned = owned if rt.copy_mode != "ce" else []
 
     def has_pending_reduce(self) -> bool:
         if self._reduce_ticket is not None:

@@ -217,12 +217,13 @@ def test_fused_forward_publish_matches_nccl():
         assert rel < 0.15, (k, rel)
 
 
-def _reduce_check_body(rank, world, fused=False, reduce_mode="backward"):
+def _reduce_check_body(rank, world, fused=False, reduce_mode="backward", copy_mode="ce"):
     import os
 
     import torch.distributed as dist
 
     os.environ["DMUON_PEER_REDUCE"] = reduce_mode
+    os.environ["DMUON_PEER_COPY"] = copy_mode
     os.environ["DMUON_DEBUG_CANARY"] = "1"          # guard bands around both arenas, verified by rt.check()
     if fused:
         os.environ["DMUON_FUSED_PUBLISH"] = "1"
@@ -269,14 +270,20 @@ def _reduce_check_body(rank, world, fused=False, reduce_mode="backward"):
             ref = dp._owned_data.to(torch.bfloat16) if dp.is_owner else torch.empty(dp._orig_size, dtype=torch.bfloat16, device=dev)
             dist.broadcast(ref, src=dp.owner_shard)
             assert torch.equal(dp._unsharded_param.data, ref), dp.fqn
-    assert rt.canary and rt.guard > 0
+    assert rt.canary and rt.guard > 0 and rt.copy_mode == ("sm" if fused else copy_mode)
     rt.check()
     return worst
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("fused,reduce_mode", [(False, "backward"), (True, "backward"), (False, "optimizer")])
-def test_peer_reduce_and_publish_are_exact(fused, reduce_mode):
+@pytest.mark.parametrize(
+    "fused,reduce_mode,copy_mode",
+    [(False, "backward", "ce"), (False, "optimizer", "ce"), (False, "backward", "sm"), (False, "optimizer", "sm"),
+     (True, "backward", "sm")],
+)
+def test_peer_reduce_and_publish_are_exact(fused, reduce_mode, copy_mode):
+    """Copy-engine transfers + local sum ("ce") and the kernels that load through the
+    peer mappings ("sm") must both deliver exactly the mean gradient and the owner's weights."""
     world = min(4, torch.cuda.device_count())
-    worst = run_ranks(_reduce_check_body, world, args=(fused, reduce_mode), backend="nccl", timeout=600)
+    worst = run_ranks(_reduce_check_body, world, args=(fused, reduce_mode, copy_mode), backend="nccl", timeout=600)
     assert max(worst) < 1e-5, worst

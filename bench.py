@@ -184,6 +184,15 @@ def make_mesh(args, world):
     return mesh, mesh, None
 
 
+def _plane_name(ctx) -> str:
+    rt = getattr(ctx, "peer_runtime", None)
+    if rt is None:
+        return "nccl"
+    if rt.copy_mode == "ce":
+        return "peer memory: copy-engine pulls and gradient gather, sum fused into the Muon prologue kernel"
+    return "peer-memory kernels (loads through peer mappings)"
+
+
 def _pred(name, p):
     return "proj" in name and p.ndim == 2
 
@@ -268,7 +277,7 @@ def build_ours(args, dims, rank, world, device):
         return MT.launch_count()
 
     ctx = getattr(model, "_dedicated_comm_ctx", None)
-    args.comm_used = "peer-memory kernels" if getattr(ctx, "peer_runtime", None) is not None else "nccl"
+    args.comm_used = _plane_name(ctx)
     return fwd_bwd, opt, launches
 
 
@@ -312,7 +321,7 @@ def build_ours_pi0(args, dims, rank, world, device):
         return MT.launch_count()
 
     ctx = getattr(model, "_dedicated_comm_ctx", None)
-    args.comm_used = "peer-memory kernels" if getattr(ctx, "peer_runtime", None) is not None else "nccl"
+    args.comm_used = _plane_name(ctx)
     return fwd_bwd, opt, launches
 
 

@@ -100,7 +100,20 @@ def local_pow_sum(grads: list[torch.Tensor], norm_type: float, device: torch.dev
     return torch.stack(norms).pow(norm_type).sum()
 
 
-def global_norm(local: torch.Tensor, norm_type: float, group=None) -> torch.Tensor:
+def _peer_plane(optimizer):
+    """The peer runtime when its ranks are the whole job (then its in-kernel
+    scalar sum can stand in for the world all-reduce of the norm)."""
+    rt = getattr(getattr(optimizer, "comm_ctx", None), "peer_runtime", None)
+    if rt is None or not (dist.is_available() and dist.is_initialized()):
+        return None
+    return rt if dist.get_world_size() == rt.world else None
+
+
+def global_norm(local: torch.Tensor, norm_type: float, group=None, optimizer=None) -> torch.Tensor:
+    rt = _peer_plane(optimizer) if (norm_type == 2.0 and local.is_cuda) else None
+    if rt is not None:
+        sums, _ = rt.scalar_allreduce(local.reshape(1))
+        return sums[0].sqrt()
     if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
         local = local.clone()
         op = dist.ReduceOp.MAX if norm_type == float("inf") else dist.ReduceOp.SUM
@@ -128,7 +141,8 @@ class GlobalNormMuonClipStrategy:
         entries = context.entries
         device = _device_of(context.optimizer, entries)
         grads = [e.grad for e in entries]
-        total = global_norm(local_pow_sum(grads, context.norm_type, device), context.norm_type)
+        total = global_norm(local_pow_sum(grads, context.norm_type, device), context.norm_type,
+                            optimizer=context.optimizer)
         if context.error_if_nonfinite and not bool(torch.isfinite(total)):
             raise RuntimeError(f"the total norm of order {context.norm_type} of the Muon gradients is non-finite")
         coef: Any = 1.0

@@ -277,6 +277,44 @@ extern "C" int dmuon_peer_pull(const DmuonPullArgs* a, void* stream_v) {
   return static_cast<int>(cudaGetLastError());
 }
 
+namespace dmuon {
+__global__ void scalar_allreduce_kernel(const DmuonScalarAllreduceArgs a) {
+  const int t = threadIdx.x;
+  const int par = a.epoch & 1;
+  float* mine = a.peer_vals[a.rank] + par * DMUON_SCALAR_MAX;
+  if (t < a.n) mine[t] = a.local[t];
+  __threadfence_system();
+  __syncwarp();
+  if (t < a.world) st_release_sys(a.peer_flags[t] + par * DMUON_MAX_PEERS + a.rank, a.epoch);
+  bool ok = true;
+  if (t < a.world) ok = wait_flag_ge_sys(a.peer_flags[a.rank] + par * DMUON_MAX_PEERS + t, a.epoch, a.budget_cycles);
+  const unsigned all_ok = __ballot_sync(0xffffffffu, ok);
+  if (all_ok != 0xffffffffu) {
+    if (t == 0) atomicCAS(a.status, 0, 4);
+    return;                                   // sums stay untouched; the host raises on the status word
+  }
+  __threadfence_system();
+  if (t < a.n) {
+    float s = 0.f;
+    for (int r = 0; r < a.world; ++r) {
+      const volatile float* v = a.peer_vals[r] + par * DMUON_SCALAR_MAX;
+      s += v[t];                              // fixed rank order: the same bits on every rank
+    }
+    a.out[t] = s;
+    if (a.coef != nullptr) a.coef[t] = fminf(1.f, a.max_norm / (sqrtf(s) + 1e-6f));
+  }
+}
+}  // namespace dmuon
+
+extern "C" int dmuon_scalar_allreduce(const DmuonScalarAllreduceArgs* a, void* stream_v) {
+  if (a->n <= 0) return 0;
+  if (a->n > DMUON_SCALAR_MAX || a->world <= 0 || a->world > DMUON_MAX_PEERS || a->rank < 0 || a->rank >= a->world)
+    return -22;
+  scalar_allreduce_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(*a);
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
+
 // One asynchronous copy on the copy engines (no SM is involved, so transfers
 // that overlap forward / backward GEMMs take nothing from them).  Either
 // pointer may be a peer mapping of another GPU's symmetric buffer.

@@ -74,6 +74,27 @@ int dmuon_wait_flags(const DmuonWaitArgs* a, void* stream);
 int dmuon_peer_prologue(const DmuonPeerPrologueArgs* a, void* stream);
 int dmuon_peer_pull(const DmuonPullArgs* a, void* stream);
 
+// Sum of a few scalars over all ranks inside one tiny kernel (gradient-clip norms):
+// every rank writes its values into its own symmetric scratch row, raises its flag
+// on every peer, waits (bounded) for all peers' flags and adds up the rows in rank
+// order, so every rank gets bit-identical sums.  Optionally turns the sums into clip
+// coefficients min(1, max_norm / (sqrt(sum) + 1e-6)).
+// Scratch per rank: vals float[2][DMUON_SCALAR_MAX], flags int[2][DMUON_MAX_PEERS];
+// the slot parity is epoch & 1 and epochs must increase by one per call on every rank.
+enum { DMUON_SCALAR_MAX = 8 };
+struct DmuonScalarAllreduceArgs {
+  float* peer_vals[DMUON_MAX_PEERS];
+  int* peer_flags[DMUON_MAX_PEERS];
+  int world, rank, n, epoch;
+  const float* local;     // n partial sums on this rank
+  float* out;             // n global sums
+  float* coef;            // optional: n clip coefficients
+  float max_norm;
+  long long budget_cycles;
+  int* status;
+};
+int dmuon_scalar_allreduce(const DmuonScalarAllreduceArgs* a, void* stream);
+
 // Copy-engine transfer (cudaMemcpyAsync, cudaMemcpyDefault); dst / src may be peer mappings.
 int dmuon_copy_async(void* dst, const void* src, long long nbytes, void* stream);
 }

@@ -65,6 +65,43 @@ def _lib():
     return lib
 
 
+SCALAR_MAX = 8
+
+
+class _ScalarAllreduceArgs(ctypes.Structure):
+    _fields_ = [
+        ("peer_vals", _PP), ("peer_flags", _PP),
+        ("world", ctypes.c_int), ("rank", ctypes.c_int), ("n", ctypes.c_int), ("epoch", ctypes.c_int),
+        ("local", ctypes.c_void_p), ("out", ctypes.c_void_p), ("coef", ctypes.c_void_p),
+        ("max_norm", ctypes.c_float), ("budget_cycles", ctypes.c_longlong), ("status", ctypes.c_void_p),
+    ]
+
+
+def scalar_allreduce(
+    peer_vals: Sequence[int], peer_flags: Sequence[int], rank: int, epoch: int, local: torch.Tensor, out: torch.Tensor,
+    status: torch.Tensor, coef: Optional[torch.Tensor] = None, max_norm: float = 0.0,
+    budget_cycles: Optional[int] = None,
+) -> None:
+    """``out[i] = sum over ranks of local[i]`` (fp32, rank order, identical bits
+    everywhere) in one single-warp kernel over symmetric scratch rows; with
+    ``coef`` also ``coef[i] = min(1, max_norm / (sqrt(out[i]) + 1e-6))``."""
+    a = _ScalarAllreduceArgs()
+    world = len(peer_vals)
+    for r in range(world):
+        a.peer_vals[r], a.peer_flags[r] = int(peer_vals[r]), int(peer_flags[r])
+    a.world, a.rank, a.n, a.epoch = world, int(rank), int(local.numel()), int(epoch)
+    assert local.dtype == out.dtype == torch.float32 and local.is_contiguous() and out.numel() >= local.numel()
+    a.local, a.out = local.data_ptr(), out.data_ptr()
+    a.coef = coef.data_ptr() if coef is not None else None
+    a.max_norm = float(max_norm)
+    a.budget_cycles = int(budget_cycles if budget_cycles is not None else wait_budget_cycles())
+    a.status = status.data_ptr()
+    fn = _lib().dmuon_scalar_allreduce
+    fn.argtypes = [ctypes.POINTER(_ScalarAllreduceArgs), ctypes.c_void_p]
+    fn.restype = ctypes.c_int
+    _check(fn(ctypes.byref(a), _stream(local.device)), "dmuon_scalar_allreduce")
+
+
 def copy_async(dst_ptr: int, src_ptr: int, nbytes: int, device: torch.device) -> None:
     """Queue one copy-engine transfer on the current stream of ``device``;
     either address may lie in a peer's symmetric buffer."""

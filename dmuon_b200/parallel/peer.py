@@ -209,6 +209,12 @@ class PeerRuntime:
             raise ValueError("DMUON_PEER_REDUCE must be 'backward' or 'optimizer'")
         for i, g in enumerate(groups):
             g._group_index = i
+        # scratch of the in-kernel scalar all-reduce (clip norms): values and flags, two parities each
+        self.sc_vals = symm_mem.empty(2 * 8, dtype=torch.float32, device=self.device)
+        self.sc_flags = symm_mem.empty(2 * MAX_PEERS, dtype=torch.int32, device=self.device)
+        self.sc_vals.zero_()
+        self.sc_flags.zero_()
+        self.sc_epoch = 0
         self.flags.zero_()
         self.grad.zero_()
         if self.canary:
@@ -223,6 +229,8 @@ class PeerRuntime:
         self.pub_ptrs = [int(p) for p in self.pub_hdl.buffer_ptrs]
         self.grad_ptrs = [int(p) for p in self.grad_hdl.buffer_ptrs]
         self.flag_ptrs = [int(p) for p in self.flag_hdl.buffer_ptrs]
+        self.sc_val_ptrs = [int(p) for p in symm_mem.rendezvous(self.sc_vals, name).buffer_ptrs]
+        self.sc_flag_ptrs = [int(p) for p in symm_mem.rendezvous(self.sc_flags, name).buffer_ptrs]
         self.status = G.status_buffer(self.device)
         self.pub_epoch = 0
         self.grad_epoch = 0
@@ -340,6 +348,21 @@ class PeerRuntime:
         from ..ops import peer as P
 
         P.wait_flags(self.flags, kind * MAX_PEERS, self.world, want, self.status)
+
+    def scalar_allreduce(self, local: torch.Tensor, max_norm: Optional[float] = None):
+        """Sum up to 8 fp32 scalars over the ranks of this plane inside one
+        kernel (symmetric scratch rows + flags, bounded wait); returns
+        ``(sums, clip_coefficients or None)``.  Every rank must call it the
+        same number of times."""
+        from ..ops import peer as P
+
+        local = local.reshape(-1).float().contiguous()
+        out = torch.empty_like(local)
+        coef = torch.empty_like(local) if max_norm is not None else None
+        self.sc_epoch += 1
+        P.scalar_allreduce(self.sc_val_ptrs, self.sc_flag_ptrs, self.rank, self.sc_epoch, local, out, self.status,
+                           coef=coef, max_norm=float(max_norm or 0.0))
+        return out, coef
 
     def check(self) -> None:
         """Synchronising status check (raises KernelTimeout when a wait gave up;

@@ -287,3 +287,40 @@ def test_peer_reduce_and_publish_are_exact(fused, reduce_mode, copy_mode):
     world = min(4, torch.cuda.device_count())
     worst = run_ranks(_reduce_check_body, world, args=(fused, reduce_mode, copy_mode), backend="nccl", timeout=600)
     assert max(worst) < 1e-5, worst
+
+
+def _scalar_body(rank, world):
+    import torch.distributed as dist
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+    from dmuon_b200.models.llama import LlamaConfig, LlamaModel
+
+    dev = torch.device("cuda", rank)
+    cfg = LlamaConfig(vocab_size=256, d_model=128, n_layers=1, n_heads=2, n_kv_heads=2, head_dim=64,
+                      ffn_hidden=256, rope_theta=10000.0)
+    with torch.device(dev):
+        model = LlamaModel(cfg).bfloat16()
+    mesh = init_device_mesh("cuda", (world,), mesh_dim_names=("dp",))
+    dmuon.dedicate_params(model, mesh, lambda n, p: "proj" in n and p.ndim == 2, comm_backend="peer")
+    fully_shard(model, mesh=mesh)
+    rt = model._dedicated_comm_ctx.peer_runtime
+    worst = 0.0
+    for it in range(5):                                    # odd count: both slot parities get reused
+        local = torch.tensor([rank + 1.0 + it, 10.0 * (rank + 1), 0.5 * it], device=dev)
+        sums, coef = rt.scalar_allreduce(local, max_norm=2.0)
+        want = local.clone()
+        dist.all_reduce(want)
+        worst = max(worst, (sums - want).abs().max().item())
+        want_coef = torch.clamp(2.0 / (want.sqrt() + 1e-6), max=1.0)
+        worst = max(worst, (coef - want_coef).abs().max().item())
+    rt.check()
+    return worst
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_in_kernel_scalar_allreduce_matches_nccl():
+    world = min(4, torch.cuda.device_count())
+    worst = run_ranks(_scalar_body, world, backend="nccl", timeout=300)
+    assert max(worst) < 1e-5, worst

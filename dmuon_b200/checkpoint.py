@@ -213,6 +213,12 @@ def set_model_state_dict(
             _load_plain(b, state_dict[name])
     if strict and missing:
         raise KeyError(f"set_model_state_dict: missing keys {missing[:8]}")
+    # peer data plane: readers hold pulled copies of the OLD weights; publish a new epoch
+    # (every rank is inside this call, so the flag protocol lines up)
+    rt = getattr(getattr(model, "_dedicated_comm_ctx", None), "peer_runtime", None)
+    if rt is not None:
+        rt.before_owner_writes()
+        rt.publish_owned()
 
 
 # --------------------------------------------------------------------------- optimizer

@@ -324,3 +324,52 @@ def test_in_kernel_scalar_allreduce_matches_nccl():
     world = min(4, torch.cuda.device_count())
     worst = run_ranks(_scalar_body, world, backend="nccl", timeout=300)
     assert max(worst) < 1e-5, worst
+
+
+def _ckpt_body(rank, world):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+    from dmuon_b200.models.llama import LlamaConfig, LlamaModel
+
+    dev = torch.device("cuda", rank)
+    cfg = LlamaConfig(vocab_size=256, d_model=128, n_layers=2, n_heads=2, n_kv_heads=2, head_dim=64,
+                      ffn_hidden=256, rope_theta=10000.0)
+    torch.manual_seed(0)
+    with torch.device(dev):
+        model = LlamaModel(cfg).bfloat16()
+    mesh = init_device_mesh("cuda", (world,), mesh_dim_names=("dp",))
+    dmuon.dedicate_params(model, mesh, lambda n, p: "proj" in n and p.ndim == 2, comm_backend="peer")
+    for layer in model.layers:
+        fully_shard(layer, mesh=mesh)
+    fully_shard(model, mesh=mesh)
+    opt = dmuon.Muon(model, lr=0.05)
+    ids = torch.randint(0, cfg.vocab_size, (2, 65), generator=torch.Generator().manual_seed(3)).to(dev)
+
+    def step():
+        opt.zero_grad()
+        model(ids[:, :-1], labels=ids[:, 1:]).backward()
+        opt.step()
+
+    def evaluate():
+        with torch.no_grad():
+            return float(model(ids[:, :-1], labels=ids[:, 1:]))
+
+    step()
+    saved = dmuon.get_model_state_dict(model, rank0_only=False)
+    at_save = evaluate()
+    step()
+    step()
+    moved = evaluate()
+    dmuon.set_model_state_dict(model, saved)
+    restored = evaluate()
+    model._dedicated_comm_ctx.peer_runtime.check()
+    return at_save, moved, restored
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_loading_a_state_dict_republishes_on_the_peer_plane():
+    for at_save, moved, restored in run_ranks(_ckpt_body, 2, backend="nccl", timeout=300):
+        assert abs(moved - at_save) > 1e-3          # training did change the weights
+        assert restored == at_save                  # and every rank reads the restored ones again

@@ -204,6 +204,61 @@ def _dp_dim_names(mesh, replicate_mesh) -> frozenset:
     return frozenset(names)
 
 
+# --------------------------------------------------------------------------- single-node HSDP on the peer plane
+class _FlatMesh:
+    """Stand-in for a 1-D mesh over every rank of a replicate x shard grid."""
+
+    def __init__(self, size: int, dim_names: tuple):
+        self._size, self.mesh_dim_names = int(size), tuple(dim_names)
+
+    def size(self) -> int:
+        return self._size
+
+    def get_group(self):
+        return dist.group.WORLD
+
+
+def _maybe_flatten_hsdp(model, mesh, replicate_mesh, predicate, comm_backend, policy_kwargs) -> Optional[_FlatMesh]:
+    """On one NVSwitch domain the two axes of an HSDP grid are the same kind of
+    link, so dedicated ownership can treat the grid as ONE data-parallel axis:
+    every rank writes its gradients into its arena, the owner gathers from all
+    R x S peers and averages once (= the two-stage mean), and every rank pulls
+    the published weights from the owner.  That is exactly the 1-D peer data
+    plane over the flattened group, so this returns a flat mesh when the peer
+    plane can take the job (all ranks of the job, at most 8, on one host, no
+    tensor parallelism, no sharded routes) and None otherwise (collective
+    two-stage implementation).  FSDP2 keeps its own 2-D mesh for everything
+    that is not dedicated."""
+    from .parallel import peer as peer_mod
+
+    want = (comm_backend or peer_mod.peer_backend_requested()).lower()
+    if want not in ("auto", "peer") or not (dist.is_available() and dist.is_initialized()):
+        return None
+    if _device_of(model).type != "cuda":
+        return None
+    world = dist.get_world_size()
+    if world != mesh.size() * replicate_mesh.size() or world > peer_mod.MAX_PEERS:
+        return None
+    if int(os.environ.get("LOCAL_WORLD_SIZE", str(torch.cuda.device_count()))) < world:
+        return None           # the grid spans hosts: the replicate axis is not NVLink
+    dp_dims = _dp_dim_names(mesh, replicate_mesh)
+    cand, names = [], {}
+    seen: set[int] = set()
+    for name, p in model.named_parameters():
+        if id(p) not in seen and predicate(name, p):
+            seen.add(id(p))
+            cand.append(p)
+            names[p] = name
+    if not cand or any(is_tp_sharded(p, dp_dims) for p in cand):
+        return None
+    pols = resolve_param_policies(params=cand, param_to_fqn=names, **policy_kwargs)
+    for p in cand:
+        pol = pols[p]
+        if (pol.route or "") == "sharded_adamw" or (pol.muon_forward_unshard or "broadcast") != "broadcast":
+            return None
+    return _FlatMesh(world, tuple(dp_dims))
+
+
 # --------------------------------------------------------------------------- shared setup
 def _setup(
     model,
@@ -244,6 +299,20 @@ def _setup(
     if muon_forward_unshard not in ("broadcast", "all_gather"):
         raise ValueError("muon_forward_unshard must be 'broadcast' or 'all_gather'")
 
+    # single-node HSDP: one flattened ownership axis on the peer plane when possible
+    hsdp_coords = None
+    user_mesh, user_replicate_mesh = mesh, replicate_mesh
+    if mode == "fsdp" and replicate_mesh is not None and replicate_mesh.size() > 1:
+        flat = _maybe_flatten_hsdp(
+            model, mesh, replicate_mesh, predicate, comm_backend,
+            dict(compute_dtype=compute_dtype, route_hint_fn=route_hint_fn, param_policy=param_policy,
+                 param_policy_fn=param_policy_fn, default_muon_forward_unshard=muon_forward_unshard),
+        )
+        if flat is not None:
+            hsdp_coords = [None] * dist.get_world_size()
+            dist.all_gather_object(hsdp_coords, (mesh.get_local_rank(), replicate_mesh.get_local_rank()))
+            mesh, replicate_mesh = flat, None
+
     assignment = compute_balanced_assignment(
         model,
         mesh,
@@ -271,7 +340,7 @@ def _setup(
     n_rep = replicate_mesh.size() if replicate_mesh is not None else 1
     _log_balance(assignment, selected, fqn_of, n_shard, n_rep, f"dedicate_params[{mode}]")
 
-    dp_dims = _dp_dim_names(mesh, replicate_mesh)
+    dp_dims = _dp_dim_names(user_mesh, user_replicate_mesh)
     if not allow_tp:
         bad = [fqn_of[p] for p in selected if is_tp_sharded(p, dp_dims)]
         if bad:
@@ -391,6 +460,10 @@ def _setup(
         ctx.peer_runtime = peer_mod.PeerRuntime(ctx, dp_group, [st.group for st in ctx.all_states])
     model._dedicated_comm_ctx = ctx
     ctx.tp_groups = list(tp_groups.values())
+    ctx.hsdp_flattened = hsdp_coords is not None
+    if hsdp_coords is not None:
+        # the caller asked for a replicate x shard grid: report owners as (shard, replicate) coordinates
+        return {p: tuple(hsdp_coords[int(o)]) for p, o in assignment.dp_owners.items()}
     return dict(assignment.dp_owners)
 
 

@@ -145,12 +145,23 @@ def _train_body(rank, world, backend, steps):
     torch.manual_seed(0)
     with torch.device(dev):
         model = LlamaModel(cfg)
-    mesh = init_device_mesh("cuda", (world,), mesh_dim_names=("dp",))
-    # fp32 gradient buffers on both data planes: with two ranks the sum is then the
-    # same number whoever computes it, so the trajectories can be compared tightly
-    dmuon.dedicate_params(model, mesh, lambda n, p: "proj" in n and p.ndim == 2,
-                          param_policy={"defaults": {"param_dtype": "bf16", "grad_dtype": "fp32"}},
-                          reshard_after_forward=False, comm_backend=backend)
+    hsdp = backend == "hsdp-flat"
+    if hsdp:
+        # a replicate x shard grid on one host: ownership is flattened onto the peer plane
+        mesh = init_device_mesh("cuda", (world, 1), mesh_dim_names=("replicate", "shard"))
+        owners = dmuon.dedicate_params(model, mesh["shard"], lambda n, p: "proj" in n and p.ndim == 2,
+                                       param_policy={"defaults": {"param_dtype": "bf16", "grad_dtype": "fp32"}},
+                                       reshard_after_forward=False, replicate_mesh=mesh["replicate"])
+        assert model._dedicated_comm_ctx.hsdp_flattened
+        assert all(isinstance(o, tuple) and o[0] == 0 and o[1] in range(world) for o in owners.values())
+        assert len({o for o in owners.values()}) == world
+    else:
+        mesh = init_device_mesh("cuda", (world,), mesh_dim_names=("dp",))
+        # fp32 gradient buffers on both data planes: with two ranks the sum is then the
+        # same number whoever computes it, so the trajectories can be compared tightly
+        dmuon.dedicate_params(model, mesh, lambda n, p: "proj" in n and p.ndim == 2,
+                              param_policy={"defaults": {"param_dtype": "bf16", "grad_dtype": "fp32"}},
+                              reshard_after_forward=False, comm_backend=backend)
     mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
     for layer in model.layers:
         fully_shard(layer, mesh=mesh, mp_policy=mp)
@@ -189,6 +200,10 @@ def test_peer_data_plane_matches_nccl():
     ref = run_ranks(_train_body, world, args=("nccl", steps), backend="nccl", timeout=600)
     got = run_ranks(_train_body, world, args=("peer", steps), backend="nccl", timeout=600)
     alt = run_ranks(_train_body, world, args=("peer-optimizer-reduce", steps), backend="nccl", timeout=600)
+    flat = run_ranks(_train_body, world, args=("hsdp-flat", steps), backend="nccl", timeout=600)
+    assert flat[0][2] and flat[0][3] == 21
+    for a, b in zip(flat[0][0], ref[0][0]):
+        assert abs(a - b) < 2e-2 * max(1.0, abs(b)), (flat[0][0], ref[0][0])
     assert not ref[0][2] and got[0][2] and alt[0][2]
     assert ref[0][3] == 0 and got[0][3] == 21 and alt[0][3] == 21      # 3 layers x 7 projections
     for a, b, c in zip(got[0][0], ref[0][0], alt[0][0]):

@@ -1,0 +1,91 @@
+"""Asynchronous post-step publish must be bit-identical to the synchronous one
+(HSDP replicate broadcast, DDP post-step broadcast), and the sharded-AdamW
+route must behave the same on a 1-D and on a replicate x shard mesh."""
+import pytest
+import torch
+
+from dist_utils import run_ranks
+from test_e2e_cpu import HP, _build_model, _data, _pred
+
+
+def _train(model, opt, rank, world, steps):
+    per = 4 // world
+    for s in range(steps):
+        x, y = _data(s)
+        x, y = x[rank * per : (rank + 1) * per], y[rank * per : (rank + 1) * per]
+        opt.zero_grad()
+        model(x, labels=y).backward()
+        opt.step()
+
+
+def _body_async(rank, world, mode, replicate_async):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+
+    model = _build_model()
+    if mode == "hsdp":
+        mesh = init_device_mesh("cpu", (2, world // 2), mesh_dim_names=("replicate", "shard"))
+        dmuon.dedicate_params(model, mesh["shard"], _pred, reshard_after_forward=False, replicate_mesh=mesh["replicate"])
+        for layer in model.layers:
+            fully_shard(layer, mesh=mesh)
+        fully_shard(model, mesh=mesh)
+    else:
+        mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("dp",))
+        dmuon.dedicate_params_ddp(model, mesh, _pred)
+        dmuon.replicate(model, mesh)
+    opt = dmuon.Muon(model, lr=HP["lr"], adamw_lr=HP["adamw_lr"], weight_decay=HP["weight_decay"],
+                     momentum=HP["momentum"], replicate_async=replicate_async, first_step_progress_log=False)
+    _train(model, opt, rank, world, 3)
+    pending = sum(1 for g in dmuon.utils.iter_groups(model) if g.has_pending_post_step())
+    dmuon.wait_all_replicate_broadcasts(model)
+    after = sum(1 for g in dmuon.utils.iter_groups(model) if g.has_pending_post_step())
+    return dmuon.get_model_state_dict(model, rank0_only=False), pending, after
+
+
+@pytest.mark.parametrize("mode", ["hsdp", "ddp"])
+def test_async_publish_is_bit_identical_to_sync(mode):
+    a = run_ranks(_body_async, 4, args=(mode, True))
+    b = run_ranks(_body_async, 4, args=(mode, False))
+    assert all(r[2] == 0 for r in a + b)                   # the drain call leaves nothing pending
+    assert all(r[1] == 0 for r in b)                       # synchronous mode never leaves an event behind
+    for r in range(4):
+        for n, t in a[r][0].items():
+            assert torch.equal(t, b[r][0][n]), (mode, r, n)
+
+
+def _body_sharded_adamw(rank, world, hsdp):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+
+    model = _build_model()
+    policy = {"overrides": [{"contains": "embed", "set": {"route": "sharded_adamw"}}]}
+    pred = lambda n, p: _pred(n, p) or "embed" in n         # noqa: E731
+    if hsdp:
+        mesh = init_device_mesh("cpu", (2, world // 2), mesh_dim_names=("replicate", "shard"))
+        dmuon.dedicate_params(model, mesh["shard"], pred, replicate_mesh=mesh["replicate"], param_policy=policy,
+                              hook_boundary_strict=False)
+        fsdp_mesh = mesh
+    else:
+        mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("dp",))
+        dmuon.dedicate_params(model, mesh, pred, param_policy=policy, hook_boundary_strict=False)
+        fsdp_mesh = mesh
+    for layer in model.layers:
+        fully_shard(layer, mesh=fsdp_mesh)
+    fully_shard(model, mesh=fsdp_mesh)
+    opt = dmuon.Muon(model, lr=HP["lr"], adamw_lr=HP["adamw_lr"], weight_decay=HP["weight_decay"],
+                     momentum=HP["momentum"], first_step_progress_log=False)
+    routes = sorted({p._dmuon_route for p in dmuon.get_dedicated_params(model)})
+    _train(model, opt, rank, world, 3)
+    return dmuon.get_model_state_dict(model, rank0_only=False), routes
+
+
+def test_sharded_adamw_route_matches_between_one_axis_and_hsdp():
+    flat = run_ranks(_body_sharded_adamw, 4, args=(False,))
+    grid = run_ranks(_body_sharded_adamw, 4, args=(True,))
+    assert flat[0][1] == grid[0][1] == ["muon", "sharded_adamw"]
+    for n, t in flat[0][0].items():
+        assert (t.float() - grid[0][0][n].float()).abs().max().item() < 5e-4, n

@@ -164,3 +164,78 @@ def test_activation_casts_at_the_hook_boundary():
         assert live == "torch.bfloat16"                    # param_dtype of the live weights
         assert masters in (["torch.float32"], [])          # fp32 masters on the owner
         assert seen and seen[0] in ("torch.float32", "torch.bfloat16")
+
+
+class ConvAsLinear(nn.Module):
+    """A kernel-size-1 Conv1d whose weight the forward squeezes and uses as a matrix."""
+
+    def __init__(self, d=16):
+        super().__init__()
+        self.mix_proj = nn.Conv1d(d, d, 1, bias=False)
+        self.out_proj = nn.Linear(d, d, bias=False)
+
+    def forward(self, x):
+        w = self.mix_proj.weight.squeeze(-1)               # direct attribute access, then a view
+        return self.out_proj(torch.tanh(F.linear(x, w)))
+
+
+def _conv_body(rank, world, steps):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+
+    torch.manual_seed(0)
+    model = nn.Sequential(ConvAsLinear(), ConvAsLinear())
+    mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("dp",))
+    dmuon.dedicate_params(model, mesh, lambda n, p: "proj" in n, reshard_after_forward=True,
+                          hook_boundary_predicate=lambda m: isinstance(m, ConvAsLinear))
+    fully_shard(model, mesh=mesh)
+    opt = dmuon.Muon(model, lr=0.05, first_step_progress_log=False)
+    x = torch.randn(4, 16, generator=torch.Generator().manual_seed(11))
+    losses = []
+    for _ in range(steps):
+        opt.zero_grad()
+        loss = model(x).pow(2).mean()
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    shapes = {p.fqn: (tuple(p.full_shape), p._dmuon_route) for p in dmuon.get_dedicated_params(model)}
+    mom = {p.fqn: tuple(opt.state[id(p)]["momentum_buffer"].shape) for p in dmuon.get_owned_params(model)}
+    return losses, shapes, mom, dmuon.get_model_state_dict(model, rank0_only=False)
+
+
+def test_three_dimensional_weights_are_orthogonalised_as_matrices():
+    import math
+
+    from dmuon_b200.optim.newton_schulz import gram_newton_schulz
+
+    steps = 3
+    torch.manual_seed(0)
+    ref = nn.Sequential(ConvAsLinear(), ConvAsLinear())
+    x = torch.randn(4, 16, generator=torch.Generator().manual_seed(11))
+    moms = {n: torch.zeros_like(p) for n, p in ref.named_parameters()}
+    ref_losses = []
+    for _ in range(steps):
+        ref.zero_grad()
+        loss = ref(x).pow(2).mean()
+        loss.backward()
+        ref_losses.append(loss.item())
+        with torch.no_grad():
+            for n, p in ref.named_parameters():
+                g2 = p.grad.reshape(p.shape[0], -1)
+                buf = moms[n].view_as(g2)
+                buf.mul_(0.95).add_(g2)
+                o = gram_newton_schulz(g2.add(buf, alpha=0.95))
+                p.add_(o.view_as(p), alpha=-0.05 * 0.2 * math.sqrt(max(g2.shape)))
+    res = run_ranks(_conv_body, 2, args=(steps,))
+    losses, shapes, _, sd = res[0]
+    assert shapes["0.mix_proj.weight"] == ((16, 16, 1), "muon")          # a 3-D weight takes the Muon route
+    owned = {}
+    for r in res:
+        owned.update(r[2])
+    assert owned["0.mix_proj.weight"] == (16, 16) and len(owned) == 4      # momentum is kept as a (rows, rest) matrix
+    for a, b in zip(losses, ref_losses):
+        assert abs(a - b) < 1e-4 * max(1.0, abs(b)), (losses, ref_losses)
+    for n, p in ref.named_parameters():
+        assert sd[n].shape == p.shape and (sd[n] - p).abs().max().item() < 2e-4, n

@@ -143,3 +143,29 @@ def test_checkpoint_roundtrip_resumes_identically(mode):
     assert names == sorted(dict(ref.named_parameters(remove_duplicate=False)))
     for a, b in zip(cont, cont2):
         assert abs(a - b) < 1e-5, (cont, cont2)
+
+
+def _body_plain_load(rank, world, mode):
+    dmuon, model, opt = _setup(rank, world, mode)
+    torch.manual_seed(123)                          # a different initialisation than the one _setup used
+    donor = _build_model()
+    plain = {k: v.detach().clone() for k, v in donor.state_dict().items()}
+    dmuon.set_model_state_dict(model, plain if rank == 0 else {}, broadcast_from_rank0=True)
+    back = dmuon.get_model_state_dict(model, rank0_only=False)
+    x, y = _data(0)
+    with torch.no_grad():
+        loss = model(x, labels=y).item()
+        want = donor(x, labels=y).item()
+    return back, plain, loss, want
+
+
+@pytest.mark.parametrize("mode", ["fsdp", "hsdp", "ddp"])
+def test_loading_a_plain_single_process_state_dict(mode):
+    """A state dict saved from an unsharded model loads into any placement
+    (only rank 0 holds it), round-trips exactly and gives the same loss."""
+    world = 4 if mode == "hsdp" else 2
+    for back, plain, loss, want in run_ranks(_body_plain_load, world, args=(mode,)):
+        assert sorted(back) == sorted(plain)
+        for k in plain:
+            assert torch.equal(back[k], plain[k]), k
+        assert abs(loss - want) < 1e-5 * max(1.0, abs(want))

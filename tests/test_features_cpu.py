@@ -266,3 +266,34 @@ def _body_pg_policy(rank, world):
 def test_process_group_policy():
     for isolated, same, shared_same in run_ranks(_body_pg_policy, 2):
         assert isolated and not same and shared_same
+
+
+def _body_profile_counters(rank, world):
+    import os
+
+    os.environ["DMUON_RECORD_FORWARD_PROFILE"] = "1"
+    try:
+        d, model, _, _ = _toy_setup(rank, world, reshard_after_forward=True)
+        opt = d.Muon(model, lr=0.05, first_step_progress_log=False)
+        ids = torch.randint(0, 32, (4, 8), generator=torch.Generator().manual_seed(rank))
+        for _ in range(2):
+            opt.zero_grad()
+            F.cross_entropy(model(ids).flatten(0, 1), ids.flatten()).backward()
+            opt.step()
+        prof = d.collect_forward_unshard_profile(model)
+        again = d.collect_forward_unshard_profile(model)          # draining resets the counters
+        post = d.utils.collect_post_step_profile(model)
+    finally:
+        os.environ.pop("DMUON_RECORD_FORWARD_PROFILE", None)
+    return prof, again, post
+
+
+def test_forward_profile_counters_are_collected_and_drained():
+    for prof, again, post in run_ranks(_body_profile_counters, 2):
+        assert prof and all(isinstance(v, dict) for v in prof.values())
+        keys = set().union(*[set(v) for v in prof.values()])
+        # Z3: every group is published for forward and again for backward, two steps -> dispatches and waits were counted
+        assert {"demand_dispatch_calls", "wait_calls", "owner_broadcast_bytes"} <= keys or "prefetch_dispatch_calls" in keys
+        total_dispatch = sum(v.get("demand_dispatch_calls", 0) + v.get("prefetch_dispatch_calls", 0) for v in prof.values())
+        assert total_dispatch >= 2 * 2 * len(prof) - 2
+        assert all(not v for v in again.values()) and isinstance(post, dict)

@@ -34,7 +34,6 @@ def main():
     import torch.nn.functional as F
 
     from dmuon_b200.ops import gemm as G
-    from dmuon_b200.ops import peer as P
     from dmuon_b200.ops import pull_linear as PL
 
     rank = int(os.environ.get("RANK", "0"))

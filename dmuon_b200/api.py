@@ -26,7 +26,7 @@ from .parallel.comm import DedicatedCommContext
 from .parallel.dgroup import DedicatedParamGroup, DedicatedParamGroupDDP
 from .parallel.dparam import DedicatedParam
 from .parallel.hooks import DedicatedState
-from .parallel.partition import compute_balanced_assignment, imbalance, layer_key
+from .parallel.partition import compute_balanced_assignment, imbalance
 from .parallel.topology import (
     get_tp_mesh,
     get_tp_shard_dim,

@@ -23,7 +23,7 @@ import logging
 import math
 import time
 from collections import defaultdict
-from typing import Any, Callable, Iterable, Optional
+from typing import Any, Callable, Optional
 
 import torch
 import torch.distributed as dist
@@ -32,11 +32,8 @@ import torch.nn as nn
 from ..policy import normalize_route
 from ..utils import (
     fence_isolated_process_groups,
-    get_comm_ctx,
     iter_groups,
-    prepare_group_muon_grads,
     prepare_muon_grads,
-    wait_group_muon_grads,
 )
 from .newton_schulz import NewtonSchulz, apply_gram_factors, gram_newton_schulz_factors
 

@@ -30,7 +30,7 @@ import torch
 import torch.distributed as dist
 from torch.profiler import record_function
 
-from .comm import DedicatedCommContext, Lane, Ticket, mark_current
+from .comm import DedicatedCommContext, Lane, Ticket
 from .dparam import DedicatedParam, alloc_storage, free_storage
 
 

@@ -18,7 +18,6 @@ accumulation included.
 """
 from __future__ import annotations
 
-from typing import Any
 
 import torch
 import torch.nn as nn

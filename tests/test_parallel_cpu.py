@@ -21,6 +21,8 @@ def _setup(rank, world, mode, reshard=False):
     if mode == "hsdp":
         mesh = init_device_mesh("cpu", (2, world // 2), mesh_dim_names=("replicate", "shard"))
         dmuon.dedicate_params(model, mesh["shard"], _pred, reshard_after_forward=reshard, replicate_mesh=mesh["replicate"], **extra)
+        # flattening the grid onto the peer plane is a single-host CUDA decision; on CPU the two-stage path runs
+        assert model._dedicated_comm_ctx.hsdp_flattened is False and model._dedicated_comm_ctx.replicate_group is not None
         for layer in model.layers:
             fully_shard(layer, mesh=mesh)
         fully_shard(model, mesh=mesh)

@@ -16,6 +16,15 @@ only what it owns:
 Constructor arguments, per-group keys, group names (``<name>/muon``,
 ``<name>/adamw``) and the update rules follow the reference
 (dmuon/optim/muon.py:127-153, :473-510, :598-638, :1674-1740, :1862-1916).
+
+Scheduling knobs of the reference that are accepted for signature parity but
+have nothing left to schedule here: ``group_prepare_ahead`` (all gradient
+transfers are complete or at least issued when ``step`` starts, and matrices
+are processed by shape, not by group), ``post_step_prefetch_sharded_adamw`` and
+``sharded_adamw_unshard_separate_stream`` (sharded-AdamW all-gathers share the
+publish lane).  ``post_step_prefetch_groups``, ``forward_prefetch_depth``,
+``replicate_async`` and the ``tp_distributed_gram*`` arguments do what their
+names say.
 """
 from __future__ import annotations
 

@@ -365,7 +365,7 @@ class DedicatedParamGroup:
         self._stage1_ticket = lane.mark()
         self._pending = packs
         ctx.last_reduced_group = self
-        if self.replicate_size > 1:
+        if self.replicate_size > 1 and not self.delay_stage2_to_optimizer:
             self._launch_stage2()
 
     def _launch_stage2(self) -> None:
@@ -393,7 +393,12 @@ class DedicatedParamGroup:
 
     def wait_for_reduce(self, lane: Optional[Lane] = None) -> None:
         """Make the reduced gradients visible as ``_reduced_grad`` on the owner
-        (ordered on ``lane`` or, by default, the current stream)."""
+        (ordered on ``lane`` or, by default, the current stream).  With
+        ``delay_stage2_to_optimizer`` (the default, as in the reference) the
+        replicate-axis reduce is issued here, i.e. when the optimizer asks for
+        the gradients, instead of inside backward."""
+        if self.replicate_size > 1 and self._stage2_ticket is None and (self._pending or self._pending_flat):
+            self._launch_stage2()
         for t in (self._stage1_ticket, self._stage2_ticket):
             if t is None:
                 continue

@@ -89,3 +89,41 @@ def test_sharded_adamw_route_matches_between_one_axis_and_hsdp():
     assert flat[0][1] == grid[0][1] == ["muon", "sharded_adamw"]
     for n, t in flat[0][0].items():
         assert (t.float() - grid[0][0][n].float()).abs().max().item() < 5e-4, n
+
+
+def _body_stage2(rank, world, delay):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+
+    model = _build_model()
+    mesh = init_device_mesh("cpu", (2, world // 2), mesh_dim_names=("replicate", "shard"))
+    dmuon.dedicate_params(model, mesh["shard"], _pred, reshard_after_forward=False, replicate_mesh=mesh["replicate"],
+                          delay_stage2_to_optimizer=delay)
+    for layer in model.layers:
+        fully_shard(layer, mesh=mesh)
+    fully_shard(model, mesh=mesh)
+    opt = dmuon.Muon(model, lr=HP["lr"], adamw_lr=HP["adamw_lr"], weight_decay=HP["weight_decay"],
+                     momentum=HP["momentum"], first_step_progress_log=False)
+    per = 4 // world
+    x, y = _data(0)
+    x, y = x[rank * per : (rank + 1) * per], y[rank * per : (rank + 1) * per]
+    opt.zero_grad()
+    model(x, labels=y).backward()
+    # right after backward: was the replicate-axis reduce already issued?
+    launched = sum(1 for g in dmuon.utils.iter_groups(model) if g._stage2_ticket is not None or (not g._pending and not g._pending_flat))
+    groups = sum(1 for _ in dmuon.utils.iter_groups(model))
+    opt.step()
+    _train(model, opt, rank, world, 2)
+    return dmuon.get_model_state_dict(model, rank0_only=False), launched, groups
+
+
+def test_replicate_axis_reduce_can_be_delayed_to_the_optimizer():
+    now = run_ranks(_body_stage2, 4, args=(False,))
+    later = run_ranks(_body_stage2, 4, args=(True,))
+    assert all(r[1] == r[2] for r in now)                    # issued inside backward for every group
+    assert all(r[1] < r[2] for r in later)                   # held back until the optimizer asks
+    for r in range(4):
+        for n, t in now[r][0].items():
+            assert torch.equal(t, later[r][0][n]), (r, n)

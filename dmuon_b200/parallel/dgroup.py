@@ -450,7 +450,12 @@ class DedicatedParamGroup:
                     lane.keep_alive(g)
                     tsize = p.tp_group.size()
                     if p.is_tp_owner:
-                        parts = [torch.empty_like(g) for _ in range(tsize)]
+                        reuse = self.comm_ctx.tp_gather_buffer_reuse_enabled()
+                        parts = getattr(p, "_tp_gather_parts", None) if reuse else None
+                        if parts is None or parts[0].shape != g.shape or parts[0].dtype != g.dtype:
+                            parts = [torch.empty_like(g) for _ in range(tsize)]
+                            if reuse:
+                                p._tp_gather_parts = parts      # kept across steps instead of re-allocated
                         for t in parts:
                             lane.keep_alive(t)
                         dist.gather(g, gather_list=parts, dst=p._tp_owner_global_rank, group=p.tp_group)
@@ -483,7 +488,11 @@ class DedicatedParamGroup:
         with lane.use(), torch.no_grad():
             with record_function(f"dmuon.tp_scatter.{self.name}"):
                 for p in todo:
-                    recv = torch.empty(p._orig_size, dtype=p._owned_data.dtype, device=self.device)
+                    recv = getattr(p, "_tp_scatter_recv", None) if self.comm_ctx.tp_scatter_buffer_reuse_enabled() else None
+                    if recv is None:
+                        recv = torch.empty(p._orig_size, dtype=p._owned_data.dtype, device=self.device)
+                        if self.comm_ctx.tp_scatter_buffer_reuse_enabled():
+                            p._tp_scatter_recv = recv
                     lane.keep_alive(recv)
                     if p.is_tp_owner:
                         delta = p._tp_full_delta.to(p._owned_data.dtype)

@@ -93,7 +93,9 @@ def _body(rank, world, mode, steps):
     for blk in model.layers:
         parallelize_module(blk, mesh["tp"], {"up_proj": ColwiseParallel(), "down_proj": RowwiseParallel()})
     if mode in ("fsdp", "fsdp_gram"):
-        owners = dmuon.dedicate_params(model, mesh["dp"], _pred, reshard_after_forward=False)
+        # the plain run also exercises reuse of the gather / scatter buffers across steps
+        owners = dmuon.dedicate_params(model, mesh["dp"], _pred, reshard_after_forward=False,
+                                       tp_buffer_reuse=(mode == "fsdp"))
         for blk in model.layers:
             fully_shard(blk, mesh=mesh["dp"])
         fully_shard(model, mesh=mesh["dp"])

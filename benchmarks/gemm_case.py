@@ -15,6 +15,60 @@ import sys
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
+def _sustain(run, seconds: float, flop_per_call: float) -> dict:
+    """Back-to-back launches for about ``seconds``; device time from CUDA events
+    around the whole train of launches, SM clock and power read through NVML
+    while it runs (reading only)."""
+    import statistics
+    import threading
+    import time
+
+    import torch
+
+    samples: list[tuple[int, float]] = []
+    stop = threading.Event()
+
+    def sampler():
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(torch.cuda.current_device())
+            while not stop.is_set():
+                samples.append((pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM),
+                                pynvml.nvmlDeviceGetPowerUsage(h) / 1000.0))
+                time.sleep(0.05)
+        except Exception:
+            pass
+
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    run()
+    torch.cuda.synchronize()
+    t0 = time.time()
+    run()
+    torch.cuda.synchronize()
+    per = max(time.time() - t0, 1e-5)
+    calls = max(8, min(20000, int(seconds / per)))
+    th = threading.Thread(target=sampler, daemon=True)
+    th.start()
+    a.record()
+    for _ in range(calls):
+        run()
+    b.record()
+    torch.cuda.synchronize()
+    stop.set()
+    th.join(timeout=1.0)
+    ms = a.elapsed_time(b)
+    tail = samples[len(samples) // 3:] or samples
+    return {
+        "calls": calls,
+        "seconds": round(ms / 1e3, 3),
+        "dense_tflops": round(flop_per_call * calls / ms / 1e9, 1),
+        "sm_mhz_median": statistics.median(c for c, _ in tail) if tail else None,
+        "power_w_median": round(statistics.median(w for _, w in tail), 1) if tail else None,
+    }
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--m", type=int, default=4096)
@@ -30,6 +84,11 @@ def main():
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--two-cta", action="store_true", help="CTA-pair kernel (cta_group::2, 256 x 256 tiles)")
+    ap.add_argument("--quad", action="store_true",
+                    help="CTA-quad kernel (two pairs per cluster share their A rows through distributed shared memory)")
+    ap.add_argument("--sustain", type=float, default=0.0,
+                    help="also run the product back to back for this many seconds and report the sustained rate "
+                         "with the SM clock and power sampled meanwhile (the regime inside a training step)")
     ap.add_argument("--cublas", action="store_true", help="also time torch.bmm on the same operands")
     args = ap.parse_args()
     import torch
@@ -53,7 +112,7 @@ def main():
 
     def run():
         G.gemm(A, B, out, a_mn=args.a_mn, b_mn=b_mn, C=C, beta=0.5 if C is not None else 0.0,
-               symmetric=args.symmetric, bn=args.bn, two_cta=args.two_cta)
+               symmetric=args.symmetric, bn=args.bn, two_cta=2 if args.quad else args.two_cta)
 
     for _ in range(args.warmup):
         run()
@@ -70,7 +129,12 @@ def main():
     G.check_status(dev)
     ms = sorted(times)[len(times) // 2]
     rec = {"M": M, "N": N, "K": K, "batch": L, "bn": args.bn, "a_mn": args.a_mn, "b_mn": b_mn,
-           "symmetric": args.symmetric, "two_cta": args.two_cta, "ms": round(ms, 4), "dense_tflops": round(2.0 * M * N * K * L / ms / 1e9, 1)}
+           "symmetric": args.symmetric, "kernel": "quad" if args.quad else ("pair" if args.two_cta else "single"),
+           "ms": round(ms, 4), "dense_tflops": round(2.0 * M * N * K * L / ms / 1e9, 1)}
+    if args.quad:
+        rec["quad_clusters"] = G.quad_max_clusters()
+    if args.sustain > 0:
+        rec["sustained"] = _sustain(run, args.sustain, 2.0 * M * N * K * L)
     if args.cublas:
         Af = A.transpose(1, 2) if args.a_mn else A
         Bf = B if b_mn else B.transpose(1, 2)
@@ -87,6 +151,8 @@ def main():
             ts.append(a.elapsed_time(b))
         rec["cublas_ms"] = round(sorted(ts)[len(ts) // 2], 4)
         rec["cublas_tflops"] = round(2.0 * M * N * K * L / rec["cublas_ms"] / 1e9, 1)
+        if args.sustain > 0:
+            rec["cublas_sustained"] = _sustain(lambda: torch.bmm(Af, Bf), args.sustain, 2.0 * M * N * K * L)
     print(json.dumps(rec))
 
 

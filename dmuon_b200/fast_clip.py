@@ -14,6 +14,8 @@ dmuon/csrc/fast_clip_kernel.cu:34-106).
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass
 from typing import Optional, Sequence
 
@@ -57,12 +59,33 @@ class SegmentedGradClipResult:
         return {s.name: s for s in self.bucket_stats}
 
 
-def _kernels_usable(device: torch.device) -> bool:
+def fast_clip_enabled() -> bool:
+    """``DMUON_FAST_CLIP=0`` sends every tensor through the PyTorch path
+    (reference toggle: dmuon/fast_clip.py:105)."""
+    return os.environ.get("DMUON_FAST_CLIP", "1").strip().lower() not in ("0", "false", "no", "off")
+
+
+def _verbose() -> bool:
+    return os.environ.get("DMUON_FAST_CLIP_VERBOSE", "0").strip().lower() in ("1", "true", "yes", "on")
+
+
+def _kernels_usable(device: torch.device) -> tuple[bool, Optional[str]]:
+    """(use the kernels?, why not).  With ``DMUON_FAST_CLIP_VERBOSE=1`` a kernel
+    library that cannot be loaded on a CUDA device raises instead of degrading
+    (reference dmuon/fast_clip.py:106-129)."""
     if device.type != "cuda":
-        return False
+        return False, "gradients are not on a CUDA device"
+    if not fast_clip_enabled():
+        return False, "disabled by DMUON_FAST_CLIP=0"
     from .ops import ns_sm100
 
-    return ns_sm100.available()
+    try:
+        ok = ns_sm100.available()
+    except Exception as exc:
+        if _verbose():
+            raise
+        return False, f"kernel library unavailable: {exc}"
+    return ok, None if ok else "sm_100a kernels unavailable on this device"
 
 
 def _local(t: torch.Tensor) -> torch.Tensor:
@@ -126,10 +149,16 @@ def clip_grad_norm_buckets_(
     process_group=None,
     chunk_size: Optional[int] = None,
 ) -> SegmentedGradClipResult:
-    del chunk_size  # the kernels pick their own grid; kept for signature parity
+    # The kernels size their own grid (one launch per ~320 tensors, 128-bit accesses), so the
+    # reference's per-job chunk length (``chunk_size`` / ``DMUON_FAST_CLIP_CHUNK_SIZE``) has nothing to
+    # tune here; both are accepted and validated so that callers and launch scripts carry over.
+    if chunk_size is None and os.environ.get("DMUON_FAST_CLIP_CHUNK_SIZE"):
+        chunk_size = int(os.environ["DMUON_FAST_CLIP_CHUNK_SIZE"])
+    if chunk_size is not None and int(chunk_size) < 1:
+        raise ValueError("chunk_size must be positive")
     buckets = tuple(buckets)
     device = _device(buckets)
-    fast = _kernels_usable(device)
+    fast, why_not = _kernels_usable(device)
     local = _local_sumsq(buckets, device, fast)
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(process_group) > 1:
         mask = torch.tensor([1.0 if b.reduce else 0.0 for b in buckets], dtype=torch.float32, device=device)
@@ -164,7 +193,7 @@ def clip_grad_norm_buckets_(
         total_norm=torch.linalg.vector_norm(norms, 2.0),
         bucket_stats=stats,
         fastpath=fast,
-        fallback_reason=None if fast else "sm_100a kernels unavailable on this device",
+        fallback_reason=why_not,
     )
 
 

@@ -51,11 +51,20 @@ struct DmuonGemmArgs {
   int max_ctas;                // 0 = one CTA per SM
   // 1: run on CTA pairs (tcgen05 cta_group::2).  The tile list is then in units
   // of 256 rows x 256 columns and bn must be 256.
+  // 2: run on clusters of two CTA pairs that share their A rows.  Each entry of
+  // the tile list then names two 256 x 256 tiles: x = m0 | m1 << 16,
+  // y = n0 | n1 << 16, z bit 0 / 1 = store tile 0 / 1 transposed as well,
+  // bit 2 = both tiles cover the same rows (m0 == m1; A is then loaded once per
+  // cluster), bit 3 = tile 1 is a filler whose result is not stored.
   int two_cta;
 };
 
 // Returns 0 on success, a cudaError_t / negative code otherwise.
 int dmuon_gemm_sm100(const DmuonGemmArgs* args, void* stream);
+
+// Clusters of four CTAs that the quad kernel can keep resident on the current
+// device (0 when the query fails; the quad path is then unavailable).
+int dmuon_gemm_quad_max_clusters(void);
 
 // Number of launches of kernels from this library since load (host counter).
 long long dmuon_launch_count(void);

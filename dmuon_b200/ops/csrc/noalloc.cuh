@@ -18,8 +18,11 @@
 //
 // Limits and rules
 //   * at most DMUON_NOALLOC_MAX_TILES (16384) output tiles per matrix; with
-//     128 x 256 tiles that is any M up to 32512.  Larger problems are rejected
-//     with DMUON_NOALLOC_E_TOO_LARGE and nothing is launched.
+//     128 x 256 tiles that is any M up to 32640 (255 rows of tiles, exactly
+//     16384 tiles).  Larger problems are rejected with
+//     DMUON_NOALLOC_E_TOO_LARGE and nothing is launched.
+//   * with batch > 1 both batch strides must be non-zero (every matrix needs
+//     its own output); otherwise DMUON_NOALLOC_E_BAD_ARGUMENT.
 //   * the first call on a device looks up the array's device address
 //     (cudaGetSymbolAddress with that device current) and sets the kernel's
 //     shared-memory attribute.  Make that first call outside any stream
@@ -53,8 +56,9 @@ enum {
 // X and D are bf16 (is_fp16 == 0) or fp16 (is_fp16 == 1); ldx / ldd are row
 // pitches in elements (multiples of 8), strides are per-matrix distances in
 // elements.  Only tiles touching the lower triangle are computed; the result
-// is stored as a full symmetric matrix.  Returns 0 or a negative code above, or
-// a positive cudaError_t from the launch.
+// is stored as a full symmetric matrix.  Returns 0, one of the negative codes
+// above, or a positive value: the cudaError_t of a failed launch or memset
+// (dmuon_syrk_noalloc_strerror gives CUDA's text for those).
 int dmuon_syrk_noalloc(const void* X, void* D, int M, int K, int batch, long long ldx, long long ldd,
                        long long strideX, long long strideD, int is_fp16, int x_mn_major, float alpha,
                        float diag, void* stream);

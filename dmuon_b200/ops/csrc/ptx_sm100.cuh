@@ -277,6 +277,50 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
                : "memory");
 }
 
+// --- operand forwarding between CTAs of one cluster (distributed shared memory) ---
+// shared memory of this CTA -> shared memory of another CTA of the cluster; the
+// bytes are counted on an mbarrier of the RECEIVING CTA.  Both addresses 16-byte
+// aligned, size a multiple of 16.  This is a copy between two SMs' shared
+// memories: no global memory and no multicast is involved.
+__device__ __forceinline__ void bulk_copy_s2cluster(uint32_t dst_cluster, uint32_t src_cta, uint32_t bytes,
+                                                    uint32_t mbar_cluster) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      :
+      : "r"(dst_cluster), "r"(src_cta), "r"(bytes), "r"(mbar_cluster)
+      : "memory");
+}
+
+// A 32-bit progress counter in another CTA's shared memory (monotonic, so a
+// reader can never confuse two rounds the way a one-bit phase could).
+__device__ __forceinline__ void st_release_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.release.cluster.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_cluster_u32(uint32_t cta_addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.cluster.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(cta_addr) : "memory");
+  return v;
+}
+
+// Spin until the counter at `cta_addr` (this CTA's shared memory, written by a
+// peer CTA) reaches `want`; gives up like mbar_wait_bounded.
+__device__ __forceinline__ bool counter_wait_bounded(uint32_t cta_addr, uint32_t want, volatile int* abort_flag) {
+  if (ld_acquire_cluster_u32(cta_addr) >= want) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (true) {
+    if (ld_acquire_cluster_u32(cta_addr) >= want) return true;
+    if ((++spins & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitBudgetCycles) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+
 // --- untiled bulk copies (16-byte aligned addresses, size a multiple of 16) ---
 // global (this GPU's or a peer's memory) -> shared, completion on an mbarrier
 __device__ __forceinline__ void bulk_load_g2s(uint32_t smem_dst, const void* gsrc, uint32_t bytes,

@@ -148,6 +148,85 @@ def tile_table(m: int, n: int, bn: int, symmetric: bool, device: torch.device, b
     return hit
 
 
+def quad_tile_list(m: int, n: int, symmetric: bool) -> list[tuple[int, int, int, int]]:
+    """Entries of the CTA-quad kernel's tile list: two 256 x 256 tiles each,
+    ``(m0 | m1 << 16, n0 | n1 << 16, flags, 0)`` with flag bits 0 / 1 = mirror
+    tile 0 / 1, bit 2 = both tiles cover the same rows (their A operand is then
+    loaded once per cluster), bit 3 = tile 1 is a filler that stores nothing.
+
+    Tiles are paired inside a row of tiles; what is left over (rows with an odd
+    number of tiles) is paired across rows without sharing, and a last single
+    tile gets a filler partner."""
+    mt, nt = (m + 255) // 256, (n + 255) // 256
+    out: list[tuple[int, int, int, int]] = []
+    left: list[tuple[int, int, int]] = []
+
+    def emit_row(i: int, cols: list[tuple[int, int]]) -> None:
+        for k in range(0, len(cols) - 1, 2):
+            (j0, f0), (j1, f1) = cols[k], cols[k + 1]
+            out.append((i | (i << 16), j0 | (j1 << 16), f0 | (f1 << 1) | 4, 0))
+        if len(cols) % 2:
+            left.append((i, cols[-1][0], cols[-1][1]))
+
+    if symmetric:
+        for i in range(mt):
+            last_row = min(m, (i + 1) * 256) - 1
+            emit_row(i, [(j, 1 if (j + 1) * 256 <= i * 256 else 0) for j in range(last_row // 256 + 1)])
+    else:
+        # column pairs outermost: clusters that run at the same time share B tiles in L2
+        for jp in range(0, nt, 2):
+            for i in range(mt):
+                emit_row(i, [(j, 0) for j in range(jp, min(jp + 2, nt))])
+    for k in range(0, len(left) - 1, 2):
+        (i0, j0, f0), (i1, j1, f1) = left[k], left[k + 1]
+        out.append((i0 | (i1 << 16), j0 | (j1 << 16), f0 | (f1 << 1), 0))
+    if len(left) % 2:
+        i0, j0, f0 = left[-1]
+        out.append((i0 | (i0 << 16), j0 | (j0 << 16), f0 | 8, 0))
+    return out
+
+
+def quad_tile_table(m: int, n: int, symmetric: bool, device: torch.device) -> tuple[torch.Tensor, int]:
+    key = ("quad", m, n, symmetric, device.index)
+    hit = _tile_cache.get(key)
+    if hit is None:
+        tiles = quad_tile_list(m, n, symmetric)
+        tab = torch.tensor([list(t) for t in tiles], dtype=torch.int32).to(device)
+        hit = (tab, len(tiles))
+        _tile_cache[key] = hit
+    return hit
+
+
+@lru_cache(maxsize=None)
+def quad_max_clusters() -> int:
+    """Clusters of four CTAs the quad kernel can keep resident on this device
+    (0: unavailable)."""
+    lib = _build.load()
+    fn = lib.dmuon_gemm_quad_max_clusters
+    fn.restype = ctypes.c_int
+    return int(fn())
+
+
+def cluster_mode() -> str:
+    """``DMUON_GEMM_CLUSTER``: ``quad`` (default; two CTA pairs per cluster share
+    their A rows through distributed shared memory) or ``pair``."""
+    import os
+
+    return os.environ.get("DMUON_GEMM_CLUSTER", "quad").strip().lower()
+
+
+def quad_kernel_pays(m: int, n: int, batch: int, symmetric: bool) -> bool:
+    """Enough tile pairs to keep every cluster busy for at least two rounds."""
+    if m < 256 or n < 512 or m > 0xFFFF * 256 or n > 0xFFFF * 256:
+        return False
+    return _quad_entries(m, n, symmetric) * batch >= 2 * 37
+
+
+@lru_cache(maxsize=None)
+def _quad_entries(m: int, n: int, symmetric: bool) -> int:
+    return len(quad_tile_list(m, n, symmetric))
+
+
 @lru_cache(maxsize=None)
 def _fn():
     lib = _build.load()
@@ -201,7 +280,7 @@ def gemm(
     b_ready: torch.Tensor | None = None,
     b_ready_epoch: int = 0,
     max_ctas: int = 0,
-    two_cta: bool | None = None,
+    two_cta: bool | int | None = None,
 ) -> torch.Tensor:
     """Launch one batched product on the current CUDA stream.
 
@@ -235,9 +314,15 @@ def gemm(
         bn = pick_bn(M, N, batch, symmetric)
     if two_cta is None:
         two_cta = TWO_CTA_DEFAULT and pair_kernel_pays(M, N, batch, symmetric)
+        if two_cta and cluster_mode() == "quad" and quad_kernel_pays(M, N, batch, symmetric) and quad_max_clusters() > 0:
+            two_cta = 2
+    two_cta = int(two_cta)
     if two_cta:
         bn = 256
-    tab, ntiles = tile_table(M, N, bn, symmetric, dev, 256 if two_cta else BM)
+    if two_cta == 2:
+        tab, ntiles = quad_tile_table(M, N, symmetric, dev)
+    else:
+        tab, ntiles = tile_table(M, N, bn, symmetric, dev, 256 if two_cta else BM)
 
     args = _GemmArgs()
     args.A = A.data_ptr()
@@ -297,7 +382,7 @@ def gemm(
         args.b_ready_epoch = int(b_ready_epoch)
     args.status = status_buffer(dev).data_ptr()
     args.max_ctas = int(max_ctas)
-    args.two_cta = int(bool(two_cta))
+    args.two_cta = two_cta
     rc = _fn()(ctypes.byref(args), ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
     if rc != 0:
         raise RuntimeError(f"dmuon_gemm_sm100 failed with code {rc}")

@@ -177,6 +177,7 @@ class Muon(torch.optim.Optimizer):
         self._last_clip_stats = None
         self._pending_gscale: Optional[torch.Tensor] = None
         self._step_count = 0
+        self._first_step_shapes_logged = 0
 
         defaults = dict(lr=lr, momentum=momentum, weight_decay=weight_decay)
         groups = self._lower_param_groups(
@@ -383,6 +384,59 @@ class Muon(torch.optim.Optimizer):
                 self.ns.backend, kern,
             )
 
+    # ------------------------------------------------------------------ first-step progress
+    def _first_step_log(self, message: str) -> None:
+        """Rank-tagged progress line of the FIRST optimizer step (stdout,
+        flushed): on a large job that step also loads the kernel library and
+        builds every per-shape workspace, so a user watching the log sees where
+        it is (the reference prints the same kind of lines around its one-time
+        kernel selection, dmuon/optim/muon.py:325-442)."""
+        if not self.first_step_progress_log:
+            return
+        if dist.is_available() and dist.is_initialized():
+            rank, world = dist.get_rank(), dist.get_world_size()
+        else:
+            rank, world = 0, 1
+        print(f"[dmuon_b200][rank={rank}/{world}] {message}", flush=True)
+
+    def _first_step_begin(self) -> Optional[float]:
+        if self._step_count != 1:
+            return None
+        self._first_step_shapes_logged = 0
+        muon = self.owned_muon_params()
+        adamw = self.owned_adamw_params()
+        rank = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+        if rank == 0 or muon or adamw:
+            shapes = {tuple(int(d) for d in dp.full_shape) for dp in muon}
+            kern = "tcgen05 sm_100a kernels" if self.device.type == "cuda" and not self.ns.deterministic else "PyTorch"
+            self._first_step_log(
+                "first optimizer step started; the kernel library is loaded and per-shape workspaces are "
+                f"allocated now (owned_muon_params={len(muon)}, owned_adamw_params={len(adamw)}, "
+                f"unique_muon_shapes={len(shapes)}, ns_backend={self.ns.backend}, ns_kernel={kern}, "
+                f"replicate_async={self.replicate_async})"
+            )
+        return time.perf_counter()
+
+    def _first_step_shape(self, rows: int, cols: int, count: int, path: str) -> None:
+        if self._step_count != 1 or self._first_step_shapes_logged >= self.first_step_progress_log_limit:
+            return
+        self._first_step_shapes_logged += 1
+        self._first_step_log(
+            f"first optimizer step: Newton-Schulz ({self.ns.backend}) on {count} matrices of shape "
+            f"{rows} x {cols}, gram_dim={min(rows, cols)}, path={path}"
+        )
+
+    def _first_step_end(self, started: Optional[float], failed: bool = False) -> None:
+        if started is None:
+            return
+        rank = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+        if rank == 0 or self.owned_muon_params() or self.owned_adamw_params():
+            what = "failed" if failed else "queued"
+            self._first_step_log(
+                f"first optimizer step {what} after {time.perf_counter() - started:.3f} s of host time"
+                + ("" if failed else "; later steps reuse the workspaces and tile tables built now")
+            )
+
     # ------------------------------------------------------------------ step
     @torch.no_grad()
     def step(self, closure: Optional[Callable[[], Any]] = None):
@@ -390,8 +444,18 @@ class Muon(torch.optim.Optimizer):
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
-        prof = _StepProfile(self.device, self.record_step_profile)
         self._step_count += 1
+        started = self._first_step_begin()
+        try:
+            self._step_impl()
+        except BaseException:
+            self._first_step_end(started, failed=True)
+            raise
+        self._first_step_end(started)
+        return loss
+
+    def _step_impl(self) -> None:
+        prof = _StepProfile(self.device, self.record_step_profile)
         groups = self._comm_groups
         gscale, self._pending_gscale = self._pending_gscale, None
 
@@ -436,7 +500,6 @@ class Muon(torch.optim.Optimizer):
                     g.unshard(prefetch=True)
         fence_isolated_process_groups()
         self._last_profile = prof if self.record_step_profile else None
-        return loss
 
     def _ensure_grads_ready(self, materialize: bool = False) -> None:
         prepare_muon_grads(self.model, coalesce_wait=True)
@@ -495,6 +558,8 @@ class Muon(torch.optim.Optimizer):
             self._step_muon_kernels(work, lr, mu, wd, gscale)
         else:
             for dp, grad in work:
+                rows = int(grad.shape[0])
+                self._first_step_shape(rows, grad.numel() // rows, 1, f"PyTorch, {dp.fqn}")
                 self._step_muon_torch(dp, grad, lr, mu, wd, gscale)
         for dp, _ in work:
             if dp.tp_group is None:
@@ -636,6 +701,7 @@ class Muon(torch.optim.Optimizer):
         restarts = self.ns.resolved_restarts()
         for (rows, cols, gdt, _od, _md, is_tp), items in by_shape.items():
             cap = ns_sm100.max_batch(rows, cols)
+            self._first_step_shape(rows, cols, len(items), "sm_100a kernels, batched by shape")
             for lo in range(0, len(items), cap):
                 chunk = items[lo : lo + cap]
                 moms = [self._momentum_of(dp, (rows, cols), self.device) for dp, _ in chunk]
@@ -729,10 +795,8 @@ class Muon(torch.optim.Optimizer):
             if dp._dmuon_route == "sharded_adamw":
                 g, p = dp._sharded_adamw_grad, dp._sharded_adamw_data
             else:
+                # (tensor-parallel parameters too: AdamW is element-wise, every TP peer updates its own shard)
                 g, p = dp._reduced_grad, dp._owned_data
-                if dp.tp_group is not None and g is not None:
-                    # element-wise optimizer: every TP peer updates its own shard
-                    pass
             if g is None or p is None:
                 continue
             st = self._adamw_state(id(dp), p, dp._optim_dtype)

@@ -675,8 +675,6 @@ class DedicatedParamGroupDDP(DedicatedParamGroup):
         with lane.use(), torch.no_grad():
             with record_function(f"dmuon.ddp_post_step_broadcast.{self.name}"):
                 for p in plist:
-                    if p.tp_group is not None and not p.is_owner:
-                        pass
                     dist.broadcast(p._owned_data, src=self._global_rank(self.dp_group, p.owner_shard), group=self.dp_group)
                 live = [p._unsharded_param for p in plist]
                 with torch.autograd._unsafe_preserve_version_counter(tuple(live)):

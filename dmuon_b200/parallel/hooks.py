@@ -24,10 +24,23 @@ import torch.nn as nn
 from torch.autograd import Variable
 
 from .comm import DedicatedCommContext
+from .dynamo import dynamo_disable
 
 
 def in_backward_pass() -> bool:
     return torch._C._current_graph_task_id() != -1
+
+
+def defer_sharded_adamw_reduce_to_root() -> bool:
+    """``DMUON_DEFER_SHARDED_ADAMW_REDUCE_TO_ROOT`` (default on): a group that
+    holds ``sharded_adamw`` parameters reduces only from the end-of-backward
+    callback.  Its reduce-scatter consumes and clears the full local gradient,
+    so it must not start while another autograd edge (a second use of the
+    module, a tied weight) can still add to it (reference
+    ``dmuon/_core/state.py:45-47,245-252``)."""
+    import os
+
+    return os.environ.get("DMUON_DEFER_SHARDED_ADAMW_REDUCE_TO_ROOT", "1") not in ("", "0", "false", "False", "FALSE")
 
 
 def _map_tensors(fn, obj):
@@ -146,6 +159,7 @@ class DedicatedState:
     def _is_first_state(self) -> bool:
         return bool(self.comm_ctx.all_states) and self.comm_ctx.all_states[0] is self
 
+    @dynamo_disable
     def _pre_forward(self, module, args, kwargs):
         ctx, group = self.comm_ctx, self.group
         recompute = in_backward_pass()
@@ -173,6 +187,7 @@ class DedicatedState:
         group._backward_done = False
         return args, kwargs
 
+    @dynamo_disable
     def _post_forward(self, module, args, output):
         group = self.group
         recompute = in_backward_pass()
@@ -188,6 +203,7 @@ class DedicatedState:
         return output
 
     # ------------------------------------------------------------------ backward
+    @dynamo_disable
     def _pre_backward(self) -> None:
         self._queue_root_callback()
         group = self.group
@@ -195,11 +211,18 @@ class DedicatedState:
         group.wait_for_unshard()
         group._backward_prefetch()
 
+    @dynamo_disable
     def _post_backward(self) -> None:
         if self._post_backward_ran:
             return
         self._queue_root_callback()
         ctx, group = self.comm_ctx, self.group
+        if (
+            not getattr(ctx, "_in_root_post_backward", False)
+            and any(p._dmuon_route == "sharded_adamw" for p in group.params)
+            and defer_sharded_adamw_reduce_to_root()
+        ):
+            return      # the root callback runs this group once the whole graph has executed
         prev = ctx.last_reduced_group
         if prev is not None and prev is not group:
             # one reduce outstanding at a time: bounds the packed-gradient memory
@@ -221,17 +244,22 @@ class DedicatedState:
         self._post_handle.remove()
 
 
+@dynamo_disable
 def _root_post_backward(ctx: DedicatedCommContext) -> None:
     """Runs once when the whole backward graph has been executed."""
-    for st in ctx.all_states:
-        if st._forward_ran and not st._post_backward_ran:
-            has_grad = any(
-                p.local_grad() is not None or getattr(p, "_grad_in_arena", False) for p in st.group.params
-            )
-            if has_grad or st.group._is_unsharded:
-                st._post_backward_ran = False
-                st._post_backward()
-        st._forward_ran = False
-        st._post_backward_ran = False
-    ctx.post_backward_final_callback_queued = False
-    ctx.last_reduced_group = None
+    ctx._in_root_post_backward = True
+    try:
+        for st in ctx.all_states:
+            if st._forward_ran and not st._post_backward_ran:
+                has_grad = any(
+                    p.local_grad() is not None or getattr(p, "_grad_in_arena", False) for p in st.group.params
+                )
+                if has_grad or st.group._is_unsharded:
+                    st._post_backward_ran = False
+                    st._post_backward()
+            st._forward_ran = False
+            st._post_backward_ran = False
+    finally:
+        ctx._in_root_post_backward = False
+        ctx.post_backward_final_callback_queued = False
+        ctx.last_reduced_group = None

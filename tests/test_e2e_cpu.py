@@ -1,10 +1,7 @@
 """End-to-end correctness on CPU: 2 gloo ranks, FSDP2 + dedicated Muon on a
 4-layer decoder with tied embeddings, against a single-process Muon."""
-import math
-
 import pytest
 import torch
-import torch.nn.functional as F
 
 from dist_utils import run_ranks
 
@@ -30,40 +27,18 @@ def _build_model():
 
 
 def oracle_run(steps=STEPS):
-    """Plain single-process Muon + AdamW with the same update rules."""
-    from dmuon_b200.optim.newton_schulz import gram_newton_schulz
+    """Single-process Muon + AdamW from ``tests/oracle.py``: the update rules
+    written out independently of the package, with a textbook float64
+    Newton-Schulz (not the package's Gram recurrence)."""
+    from oracle import muon_adamw_run
 
     model = _build_model()
-    params = dict(model.named_parameters())
-    mom = {n: torch.zeros_like(p) for n, p in params.items() if _pred(n, p)}
-    adam = {n: dict(m=torch.zeros_like(p), v=torch.zeros_like(p), t=0) for n, p in params.items() if not _pred(n, p)}
-    losses = []
-    for s in range(steps):
-        x, y = _data(s)
-        loss = model(x, labels=y)
-        model.zero_grad()
-        loss.backward()
-        losses.append(loss.item())
-        with torch.no_grad():
-            for n, p in params.items():
-                g = p.grad
-                if n in mom:
-                    buf = mom[n]
-                    buf.mul_(HP["momentum"]).add_(g)
-                    u = g.add(buf, alpha=HP["momentum"])
-                    o = gram_newton_schulz(u)
-                    p.mul_(1 - HP["lr"] * HP["weight_decay"])
-                    p.add_(o, alpha=-HP["lr"] * 0.2 * math.sqrt(max(p.shape)))
-                else:
-                    st = adam[n]
-                    st["t"] += 1
-                    b1, b2 = HP["betas"]
-                    p.mul_(1 - HP["adamw_lr"] * HP["adamw_wd"])
-                    st["m"].mul_(b1).add_(g, alpha=1 - b1)
-                    st["v"].mul_(b2).addcmul_(g, g, value=1 - b2)
-                    denom = (st["v"].sqrt() / math.sqrt(1 - b2 ** st["t"])).add_(HP["eps"])
-                    p.addcdiv_(st["m"], denom, value=-HP["adamw_lr"] / (1 - b1 ** st["t"]))
-    return losses, {n: p.detach().clone() for n, p in params.items()}
+    losses = muon_adamw_run(
+        model, _pred, [_data(s) for s in range(steps)], lambda m, b: m(b[0], labels=b[1]),
+        lr=HP["lr"], momentum=HP["momentum"], weight_decay=HP["weight_decay"], adamw_lr=HP["adamw_lr"],
+        adamw_wd=HP["adamw_wd"], betas=HP["betas"], eps=HP["eps"],
+    )
+    return losses, {n: p.detach().clone() for n, p in model.named_parameters()}
 
 
 def _dist_body(rank, world, reshard, steps):

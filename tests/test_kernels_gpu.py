@@ -91,6 +91,33 @@ PAIR_CASES = [
 @pytest.mark.parametrize("case", PAIR_CASES, ids=[f"pair{i}" for i in range(len(PAIR_CASES))])
 def test_gemm_pair_kernel_matches_fp32(case):
     """CTA-pair kernel (tcgen05 cta_group::2, 256 x 256 tiles)."""
+    _run_cluster_case(case, 1)
+
+
+QUAD_CASES = PAIR_CASES + [
+    # one shared pair of tiles per row, K of a single block
+    (256, 512, 64, 1, False, False, False, torch.bfloat16, False),
+    # three column tiles per row: shared pairs plus unshared left-overs, odd total -> a filler tile
+    (768, 768, 2368, 1, False, False, False, torch.bfloat16, True),
+    # many k-blocks (several trips around the stage ring), both operand layouts, batch
+    (512, 1024, 4096, 2, False, True, False, torch.bfloat16, False),
+    (1024, 1024, 1472, 2, True, True, True, torch.bfloat16, True),
+    # larger symmetric product, fp16 operands, batch 3
+    (2048, 2048, 1024, 3, False, False, True, torch.float16, True),
+]
+
+
+@pytest.mark.parametrize("case", QUAD_CASES, ids=[f"quad{i}" for i in range(len(QUAD_CASES))])
+def test_gemm_quad_kernel_matches_fp32(case):
+    """CTA-quad kernel: two CTA pairs per cluster, A rows forwarded between the
+    pairs through distributed shared memory."""
+    from dmuon_b200.ops import gemm as G
+
+    assert G.quad_max_clusters() > 0
+    _run_cluster_case(case, 2)
+
+
+def _run_cluster_case(case, two_cta):
     from dmuon_b200.ops import gemm as G
 
     M, N, K, batch, a_mn, b_mn, sym, odt, epi = case
@@ -113,7 +140,7 @@ def test_gemm_pair_kernel_matches_fp32(case):
         C = C.to(odt)
         alpha, beta, diag = 1.5, -0.5, (0.3 if M == N else 0.0)
     out = torch.full((batch, M, N), float("nan"), device=dev, dtype=odt)
-    G.gemm(A, B, out, a_mn=a_mn, b_mn=b_mn, C=C, alpha=alpha, beta=beta, diag=diag, symmetric=sym, two_cta=True)
+    G.gemm(A, B, out, a_mn=a_mn, b_mn=b_mn, C=C, alpha=alpha, beta=beta, diag=diag, symmetric=sym, two_cta=two_cta)
     torch.cuda.synchronize()
     G.check_status(dev)
     ref = _ref_gemm(A, B, a_mn, b_mn, C, alpha, beta, diag)

@@ -256,3 +256,57 @@ def test_bucket_clip_semantics_on_cpu():
     assert bool(r2.bucket_stats[0].found_inf) and not bool(r2.bucket_stats[0].clipped)
     r3 = clip_grad_norm_buckets_([GradClipBucket("x", g)], 1.0)
     assert bool(r3.bucket_stats[0].found_inf) and not bool(r3.bucket_stats[0].clipped)
+
+
+@pytest.mark.parametrize("m,n,sym", [(4096, 4096, True), (1152, 1152, True), (256, 256, True), (768, 1792, False),
+                                     (4096, 14336, False), (300, 700, False), (2048, 2048, True)])
+def test_quad_tile_list_covers_the_pair_tile_list_exactly(m, n, sym):
+    """The two-tiles-per-entry list of the CTA-quad GEMM names every 256 x 256
+    tile of the CTA-pair list exactly once, with the same mirror flags; entries
+    marked as sharing rows do share them; at most one filler."""
+    from dmuon_b200.ops import gemm as G
+
+    want = G.symmetric_tiles(m, 256, 256) if sym else G.dense_tiles(m, n, 256, 256)
+    got, fillers = [], 0
+    for x, y, z, _ in G.quad_tile_list(m, n, sym):
+        m0, m1, n0, n1 = x & 0xFFFF, x >> 16, y & 0xFFFF, y >> 16
+        got.append((m0, n0, z & 1))
+        if z & 8:
+            fillers += 1
+            assert (m1, n1) == (m0, n0) and not z & 4
+        else:
+            got.append((m1, n1, (z >> 1) & 1))
+        if z & 4:
+            assert m0 == m1 and n0 != n1
+    assert fillers <= 1
+    assert sorted(got) == sorted(want)
+
+
+@pytest.mark.parametrize("shape", [(64, 128), (128, 64), (96, 96), (32, 256)])
+@pytest.mark.parametrize("formulation", ["gram", "direct"])
+def test_newton_schulz_against_svd_polar_factor_and_textbook_iteration(shape, formulation):
+    """Pins the specification with two things the package did not write: the
+    polar factor ``U V^T`` from an SVD (Newton-Schulz must share its singular
+    vectors and push every singular value near 1) and a float64 textbook
+    quintic iteration on the matrix itself (``tests/oracle.py``)."""
+    from oracle import newton_schulz_reference
+
+    from dmuon_b200.optim.newton_schulz import direct_newton_schulz, gram_newton_schulz
+
+    torch.manual_seed(3)
+    G = torch.randn(*shape)
+    O = gram_newton_schulz(G) if formulation == "gram" else direct_newton_schulz(
+        G, steps=5, compute_dtype=torch.float32)
+    U, S, Vh = torch.linalg.svd(G.double(), full_matrices=False)
+    core = U.T @ O.double() @ Vh.T              # diagonal iff O = U f(S) V^T
+    diag = torch.diag(core)
+    off = core - torch.diag(diag)
+    assert off.abs().max().item() < 1e-4
+    assert -1e-4 < diag.min().item() and diag.max().item() < 1.25      # singular values only move towards 1
+    if shape[0] != shape[1]:
+        # a rectangular Gaussian matrix is well conditioned: five steps bring every singular value near 1
+        # (a square one has singular values near 0, which five steps cannot lift)
+        assert diag.min().item() > 0.5
+        small = O if shape[0] < shape[1] else O.T
+        assert (small @ small.T - torch.eye(small.shape[0])).abs().max().item() < 0.3
+    assert (O - newton_schulz_reference(G)).abs().max().item() < 2e-5

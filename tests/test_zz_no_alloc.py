@@ -58,17 +58,24 @@ def test_no_alloc_entry_matches_regular_entry_twice_in_a_row():
         dict(M=1152, K=2048, batch=3, dtype=torch.bfloat16, mn=False, alpha=0.75, diag=0.5),
         dict(M=640, K=1024, batch=2, dtype=torch.float16, mn=True, alpha=1.25, diag=0.0),
     ]
-    for c in cases:
+    for n, c in enumerate(cases):
         M, K, L = c["M"], c["K"], c["batch"]
         X = (torch.randn(L, K, M, device=dev) if c["mn"] else torch.randn(L, M, K, device=dev)).mul_(0.05).to(c["dtype"])
         want = torch.empty(L, M, M, device=dev, dtype=c["dtype"])
         G.gemm(X, X, want, a_mn=c["mn"], b_mn=c["mn"], alpha=c["alpha"], diag=c["diag"], symmetric=True, bn=256)
         got = torch.full((L, M, M), float("nan"), device=dev, dtype=c["dtype"])
+        torch.cuda.synchronize(dev)
         before = torch.cuda.memory_allocated(dev)
+        free_before, _ = torch.cuda.mem_get_info(dev)
         rc = _call(fn, X, got, M, K, L, c["mn"], c["alpha"], c["diag"])
         assert rc == 0, lib.dmuon_syrk_noalloc_strerror(rc)
         assert lib.dmuon_syrk_noalloc_status(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)) == 0
         assert torch.cuda.memory_allocated(dev) == before
+        if n > 0:
+            # torch's counter cannot see a raw cudaMalloc; the driver's free-memory figure can.  Only
+            # checked from the second call on: the first one may make the driver load the kernels.
+            free_after, _ = torch.cuda.mem_get_info(dev)
+            assert free_after >= free_before
         G.check_status(dev)
         scale = want.float().abs().max().item() + 1e-6
         assert not torch.isnan(got.float()).any()
@@ -91,5 +98,9 @@ def test_no_alloc_entry_rejects_what_does_not_fit():
     # pitch that is not a multiple of 8 elements
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     rc = fn(ctypes.c_void_p(X.data_ptr()), ctypes.c_void_p(D.data_ptr()), 128, 64, 1, 60, 128, 0, 0, 0, 0, 1.0, 0.0, stream)
+    assert rc == -1
+    # two matrices that would share one output (zero batch stride)
+    X2 = torch.zeros(2, 128, 64, device=dev, dtype=torch.bfloat16)
+    rc = fn(ctypes.c_void_p(X2.data_ptr()), ctypes.c_void_p(D.data_ptr()), 128, 64, 2, 64, 128, 128 * 64, 0, 0, 0, 1.0, 0.0, stream)
     assert rc == -1
     assert float(D.abs().sum()) == 0.0

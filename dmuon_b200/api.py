@@ -379,6 +379,25 @@ def _setup(
         default_muon_forward_unshard=muon_forward_unshard,
     )
 
+    # Replicated placement on one NVSwitch domain: the dedicated matrices take the peer-memory plane in
+    # its FSDP form (bf16 copies in every rank's publish arena, masters and momentum on the owner only, the
+    # owner's update stored to all ranks, gradients reduced from the arenas); ``replicate`` keeps averaging
+    # the other parameters.  What a replicated placement promises -- every rank holds the whole weight for
+    # forward and backward, one owner updates it -- holds unchanged; the fp32 post-step broadcast
+    # (reference dmuon/_backends/ddp/group.py:565-603) has nothing left to send.
+    ddp_on_peer = False
+    if mode == "ddp":
+        from .parallel import peer as peer_mod0
+
+        want0 = (comm_backend or peer_mod0.peer_backend_requested()).lower()
+        if want0 in ("auto", "peer"):
+            why0 = peer_mod0.peer_backend_possible_from_policies(
+                device, dp_group, rep_group, selected, policies, lambda q: is_tp_sharded(q, dp_dims))
+            if why0 is None:
+                ddp_on_peer, mode, reshard_after_forward = True, "fsdp", False
+            elif want0 == "peer":
+                raise RuntimeError(f"comm_backend='peer' is not possible here: {why0}")
+
     grouped: dict[tuple, list[DedicatedParam]] = defaultdict(list)
     for p in selected:
         sites = index.sites[id(p)]
@@ -459,6 +478,13 @@ def _setup(
     if use_peer:
         ctx.peer_runtime = peer_mod.PeerRuntime(ctx, dp_group, [st.group for st in ctx.all_states])
     model._dedicated_comm_ctx = ctx
+    ctx.ddp_on_peer_plane = ddp_on_peer
+    if ddp_on_peer:
+        ctx.mode = "ddp"
+        for st in ctx.all_states:
+            for dpar in st.group.params:
+                dpar._unsharded_param._dedicated_mode = "ddp"
+                dpar._placeholder._dedicated_mode = "ddp"
     ctx.tp_groups = list(tp_groups.values())
     ctx.hsdp_flattened = hsdp_coords is not None
     if hsdp_coords is not None:
@@ -557,10 +583,18 @@ def dedicate_params_ddp(
     param_policy=None,
     param_policy_fn=None,
     process_group_policy: Optional[str] = None,
+    comm_backend: Optional[str] = None,
 ) -> dict:
     """Replicated (DDP-style) placement: every rank keeps the live parameter,
     gradients are reduced to the owner, the owner's update is broadcast after
-    the step.  Use together with :func:`replicate` for the other parameters."""
+    the step.  Use together with :func:`replicate` for the other parameters.
+
+    ``comm_backend`` (``auto`` / ``peer`` / ``nccl``, default from
+    ``DMUON_COMM_BACKEND``): on one NVSwitch domain the dedicated matrices use
+    the peer-memory data plane -- every rank holds the bf16 weights in its
+    publish arena, the owner's update kernel stores the new weights to all of
+    them and gradients are reduced out of the ranks' arenas -- instead of NCCL
+    reduce / broadcast."""
     if getattr(mesh, "ndim", 1) != 1:
         raise ValueError("dedicate_params_ddp expects a 1-D data-parallel mesh")
     return _setup(
@@ -583,6 +617,7 @@ def dedicate_params_ddp(
         param_policy_fn=param_policy_fn,
         process_group_policy=process_group_policy,
         allow_tp=False,
+        comm_backend=comm_backend,
     )
 
 

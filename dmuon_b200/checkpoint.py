@@ -185,9 +185,23 @@ def set_model_state_dict(
     missing = []
     device = getattr(getattr(model, "_dedicated_comm_ctx", None), "device", torch.device("cpu"))
 
+    bcast = broadcast_from_rank0 and _dist_on()
+    present: Optional[dict[str, bool]] = None
+    if bcast:
+        # rank 0 tells everybody which names it holds, so that all ranks skip the same ones and no rank is
+        # left waiting in a broadcast that rank 0 never enters
+        names = [n for n, _ in model.named_parameters(remove_duplicate=False)]
+        names += [n for n, _ in model.named_buffers(remove_duplicate=False)]
+        mask = torch.tensor([1 if (_rank() == 0 and n in state_dict) else 0 for n in names], dtype=torch.int32,
+                            device=device)
+        dist.broadcast(mask, src=0)
+        present = {n: bool(v) for n, v in zip(names, mask.tolist())}
+
     def fetch(name: str, shape, dtype) -> Optional[torch.Tensor]:
-        if not broadcast_from_rank0 or not _dist_on():
+        if not bcast:
             return state_dict.get(name)
+        if not present.get(name, False):
+            return None
         t = state_dict[name].to(device=device, dtype=dtype) if _rank() == 0 else torch.empty(shape, dtype=dtype, device=device)
         dist.broadcast(t, src=0)
         return t
@@ -208,9 +222,14 @@ def set_model_state_dict(
             _load_dedicated(dp, full)
         else:
             _load_plain(p, full)
+    seen_buffers: set[int] = set()
     for name, b in model.named_buffers(remove_duplicate=False):
-        if name in state_dict and not broadcast_from_rank0:
-            _load_plain(b, state_dict[name])
+        if id(b) in seen_buffers:
+            continue
+        full = fetch(name, b.shape, b.dtype)
+        if full is not None:
+            seen_buffers.add(id(b))
+            _load_plain(b, full)
     if strict and missing:
         raise KeyError(f"set_model_state_dict: missing keys {missing[:8]}")
     # peer data plane: readers hold pulled copies of the OLD weights; publish a new epoch
@@ -362,8 +381,18 @@ def set_optimizer_state_dict(model: nn.Module, optimizer, state_dict: dict[str, 
         if dp.is_owner and (dp.tp_group is None or dp.is_tp_owner):
             state[id(dp)]["momentum_buffer"] = buf.to(device=dp.device, dtype=dp._optim_dtype).clone()
         if dp.tp_group is not None and dp.is_owner:
-            full = buf.to(dp.device).view(dp.full_shape)
-            state[id(dp)]["tp_local_momentum_buffer"] = _tp_slice(dp, full).to(dp._optim_dtype).clone()
+            # this rank's part of the (rows, rest) momentum MATRIX, the shape the distributed-Gram step adds
+            # its 2-D local gradient to (parameters with more than two dimensions included)
+            rows = int(dp.full_shape[0])
+            full = buf.to(dp.device).reshape(rows, -1)
+            tp_rank, tp_size = dp.tp_group.rank(), dp.tp_group.size()
+            if dp.shard_dim == 0:
+                per = rows // tp_size
+                local = full.narrow(0, tp_rank * per, per)
+            else:
+                per = full.shape[1] // tp_size
+                local = full.narrow(1, tp_rank * per, per)
+            state[id(dp)]["tp_local_momentum_buffer"] = local.to(dp._optim_dtype).contiguous().clone()
     for fqn, entry in state_dict.get("dedicated_adamw", {}).items():
         dp = by_fqn.get(fqn)
         if dp is None:

@@ -66,6 +66,7 @@ struct KParams {
   const int* b_ready;
   int b_ready_epoch;
   int* status;
+  int d2_multimem;
 };
 
 // ---- epilogue helpers -------------------------------------------------------
@@ -126,6 +127,22 @@ __device__ __forceinline__ void store_row32(T* dst, const float (&v)[32], int nv
   }
 }
 
+// bf16 row chunk to a multicast address: every rank's copy of the buffer
+// receives it (multimem.st through the switch).  The host only selects this
+// path when every row start is 16-byte aligned and N is a multiple of 8.
+__device__ __forceinline__ void store_row32_multicast(__nv_bfloat16* mc_dst, const float (&v)[32], int nvalid) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (i * 8 < nvalid) {
+      uint4 raw;
+      __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) e[j] = __float2bfloat16_rn(v[i * 8 + j]);
+      multimem_st_16B(mc_dst + i * 8, raw);
+    }
+  }
+}
+
 template <typename T>
 __device__ __forceinline__ void store_col32(T* dst, long long ld, const float (&v)[32], int nvalid) {
   // dst points at element (col0, row) of the transposed tile; consecutive
@@ -162,7 +179,9 @@ __device__ __forceinline__ void epilogue_chunk(const KParams& p, const T* Cb, T*
     store_row32<T>(dst, v, nvalid, vec);
     if (mirror) store_col32<T>(Db + static_cast<long long>(col0) * p.ldd + row, p.ldd, v, nvalid);
   }
-  if (D2b != nullptr) {
+  if (D2b != nullptr && p.d2_multimem) {
+    store_row32_multicast(D2b + static_cast<long long>(row) * p.ldd2 + col0, v, nvalid);
+  } else if (D2b != nullptr) {
     __nv_bfloat16* dst = D2b + static_cast<long long>(row) * p.ldd2 + col0;
     const bool vec = ((p.ldd2 * 2) % 16 == 0) && ((reinterpret_cast<uintptr_t>(D2b) & 15) == 0);
     store_row32<__nv_bfloat16>(dst, v, nvalid, vec);
@@ -1055,6 +1074,7 @@ static KParams make_params(const DmuonGemmArgs& a) {
   p.out_kind = a.out_kind;
   p.b_ready = a.b_ready; p.b_ready_epoch = a.b_ready_epoch;
   p.status = a.status;
+  p.d2_multimem = a.d2_multimem;
   if (p.C == nullptr && p.C_tab == nullptr) p.beta = 0.f;
   return p;
 }
@@ -1185,6 +1205,10 @@ extern "C" int dmuon_gemm_sm100(const DmuonGemmArgs* args, void* stream_v) {
   if ((a.bn != 128 && a.bn != 256) || a.tile_tab == nullptr || a.tiles_per_batch <= 0) return -1;
   if ((a.lda % 8) != 0 || (a.ldb % 8) != 0 || (a.strideA % 8) != 0 || (a.strideB % 8) != 0) return -1;
   if ((reinterpret_cast<uintptr_t>(a.A) & 15) || (reinterpret_cast<uintptr_t>(a.B) & 15)) return -1;
+  // the multicast form of the second output writes whole 16-byte groups of a row and has no transposed store
+  if (a.d2_multimem && ((a.N % 8) != 0 || (a.ldd2 % 8) != 0 || (a.strideD2 % 8) != 0 ||
+                        (reinterpret_cast<uintptr_t>(a.D2) & 15)))
+    return -1;
   static int num_sms[16] = {};
   int dev = 0;
   cudaGetDevice(&dev);

@@ -57,6 +57,12 @@ struct DmuonGemmArgs {
   // bit 2 = both tiles cover the same rows (m0 == m1; A is then loaded once per
   // cluster), bit 3 = tile 1 is a filler whose result is not stored.
   int two_cta;
+  // 1: D2 / D2_tab hold addresses in the NVSwitch MULTICAST mapping of a symmetric
+  // buffer: the bf16 copy is written with multimem.st and lands at the same offset
+  // of every rank's buffer (the owner's publish becomes part of the product that
+  // computes the new weights).  Needs N, ldd2 and strideD2 multiples of 8, 16-byte
+  // aligned bases (every table entry too), and a tile list without mirror flags.
+  int d2_multimem;
 };
 
 // Returns 0 on success, a cudaError_t / negative code otherwise.

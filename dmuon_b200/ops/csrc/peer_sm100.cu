@@ -213,11 +213,54 @@ __global__ void __launch_bounds__(kBlock) peer_pull_kernel(const DmuonPullArgs a
   for (; i < n16; i += stride) dst[i] = src[i];
 }
 
+// mode 0: local <- in-switch sum over all ranks; mode 1: all ranks <- local.
+template <int kDtype>
+__global__ void __launch_bounds__(kBlock) multicast_copy_kernel(const DmuonMulticastArgs a) {
+  const int t = blockIdx.y;
+  const long long n16 = a.nbytes[t] >> 4;
+  const long long stride = static_cast<long long>(gridDim.x) * kBlock;
+  long long i = static_cast<long long>(blockIdx.x) * kBlock + threadIdx.x;
+  if (a.mode == 0) {
+    const uint4* src = reinterpret_cast<const uint4*>(a.src[t]);
+    uint4* dst = reinterpret_cast<uint4*>(a.dst[t]);
+    auto ldr = [](const uint4* p) {
+      if constexpr (kDtype == DMUON_BF16) return multimem_ld_reduce_bf16x8(p);
+      else if constexpr (kDtype == DMUON_FP16) return multimem_ld_reduce_f16x8(p);
+      else return multimem_ld_reduce_f32x4(p);
+    };
+    // four independent reduce-loads in flight per thread
+    for (; i + 3 * stride < n16; i += 4 * stride) {
+      const uint4 v0 = ldr(src + i), v1 = ldr(src + i + stride), v2 = ldr(src + i + 2 * stride),
+                  v3 = ldr(src + i + 3 * stride);
+      dst[i] = v0; dst[i + stride] = v1; dst[i + 2 * stride] = v2; dst[i + 3 * stride] = v3;
+    }
+    for (; i < n16; i += stride) dst[i] = ldr(src + i);
+  } else {
+    const uint4* src = reinterpret_cast<const uint4*>(a.src[t]);
+    uint4* dst = reinterpret_cast<uint4*>(a.dst[t]);
+    for (; i < n16; i += stride) multimem_st_16B(dst + i, src[i]);
+  }
+}
+
+static int sm_count() {
+  static int cached[16] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 16) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 static int grid_x(long long max_items, int ntensors, int override_blocks) {
   if (override_blocks > 0) return override_blocks;
+  const long long sms = sm_count();
   long long need = (max_items + kBlock - 1) / kBlock;
-  long long cap = (148LL * 4 + ntensors - 1) / ntensors;
-  if (cap < 148LL * 2) cap = 148LL * 2;
+  long long cap = (sms * 4 + ntensors - 1) / ntensors;
+  if (cap < sms * 2) cap = sms * 2;
   long long b = need < cap ? need : cap;
   return static_cast<int>(b < 1 ? 1 : b);
 }
@@ -273,6 +316,27 @@ extern "C" int dmuon_peer_pull(const DmuonPullArgs* a, void* stream_v) {
   }
   dim3 grid(grid_x(mx >> 4, a->n, a->blocks_per_tensor), a->n);
   peer_pull_kernel<<<grid, kBlock, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(*a);
+  count_launch();
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int dmuon_multicast_copy(const DmuonMulticastArgs* a, void* stream_v) {
+  if (a->n <= 0) return 0;
+  if (a->n > DMUON_MAX_TENSORS || (a->mode != 0 && a->mode != 1)) return -1;
+  long long mx = 0;
+  for (int i = 0; i < a->n; ++i) {
+    if ((a->nbytes[i] & 15) || (reinterpret_cast<uintptr_t>(a->src[i]) & 15) ||
+        (reinterpret_cast<uintptr_t>(a->dst[i]) & 15))
+      return -1;
+    mx = a->nbytes[i] > mx ? a->nbytes[i] : mx;
+  }
+  dim3 grid(grid_x(mx >> 4, a->n, a->blocks_per_tensor), a->n);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_v);
+  switch (a->dtype) {
+    case DMUON_BF16: multicast_copy_kernel<DMUON_BF16><<<grid, kBlock, 0, st>>>(*a); break;
+    case DMUON_FP16: multicast_copy_kernel<DMUON_FP16><<<grid, kBlock, 0, st>>>(*a); break;
+    default: multicast_copy_kernel<DMUON_FP32><<<grid, kBlock, 0, st>>>(*a); break;
+  }
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }

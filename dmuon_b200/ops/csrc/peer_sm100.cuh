@@ -1,6 +1,7 @@
 // Kernels that move dedicated-parameter data between GPUs with plain peer
-// loads and stores on NVSwitch-mapped symmetric buffers (no library
-// collective, no multicast load), fused with the adjacent elementwise work.
+// loads and stores on NVSwitch-mapped symmetric buffers, or with multimem
+// reduce-loads / stores on their multicast mapping (no library collective, no
+// TMA), fused with the adjacent elementwise work.
 #pragma once
 #include <stdint.h>
 
@@ -94,6 +95,24 @@ struct DmuonScalarAllreduceArgs {
   int* status;
 };
 int dmuon_scalar_allreduce(const DmuonScalarAllreduceArgs* a, void* stream);
+
+// NVSwitch multicast transfers (NVLS).  `mc` addresses lie in the multicast
+// mapping of a symmetric buffer: the same offset of every rank's buffer.
+//   mode 0  reduce:     dst[t] (local)       = sum over ranks of mc_src[t], formed in the switch
+//                       (element type `dtype`; 16-bit types accumulate in fp32 and round once)
+//   mode 1  broadcast:  every rank's mc_dst[t] = src[t] (local)
+// Sizes in bytes, multiples of 16; all addresses 16-byte aligned.  The caller
+// orders these against the other ranks with the flag kernels above.
+struct DmuonMulticastArgs {
+  const void* src[DMUON_MAX_TENSORS];
+  void* dst[DMUON_MAX_TENSORS];
+  long long nbytes[DMUON_MAX_TENSORS];
+  int n;
+  int mode;
+  int dtype;                             // DMUON_FP32 / DMUON_BF16 / DMUON_FP16 (mode 0 only)
+  int blocks_per_tensor;                 // 0 = default
+};
+int dmuon_multicast_copy(const DmuonMulticastArgs* a, void* stream);
 
 // Copy-engine transfer (cudaMemcpyAsync, cudaMemcpyDefault); dst / src may be peer mappings.
 int dmuon_copy_async(void* dst, const void* src, long long nbytes, void* stream);

@@ -65,6 +65,7 @@ class _GemmArgs(ctypes.Structure):
         ("status", ctypes.c_void_p),
         ("max_ctas", ctypes.c_int),
         ("two_cta", ctypes.c_int),
+        ("d2_multimem", ctypes.c_int),
     ]
 
 
@@ -208,11 +209,16 @@ def quad_max_clusters() -> int:
 
 
 def cluster_mode() -> str:
-    """``DMUON_GEMM_CLUSTER``: ``quad`` (default; two CTA pairs per cluster share
-    their A rows through distributed shared memory) or ``pair``."""
+    """``DMUON_GEMM_CLUSTER``: ``pair`` (default: one ``cta_group::2`` pair per
+    256 x 256 tile) or ``quad`` (two pairs per cluster share their A rows
+    through distributed shared memory: 0.75 x the L2 reads per tile, but the
+    load -> forward -> consume chain is longer than the seven stages that fit
+    in shared memory can cover, and only 33 clusters of four fit on 148 SMs;
+    measured 3-4 x slower than pairs on a B200, kept as an option and a test
+    subject)."""
     import os
 
-    return os.environ.get("DMUON_GEMM_CLUSTER", "quad").strip().lower()
+    return os.environ.get("DMUON_GEMM_CLUSTER", "pair").strip().lower()
 
 
 def quad_kernel_pays(m: int, n: int, batch: int, symmetric: bool) -> bool:
@@ -281,6 +287,7 @@ def gemm(
     b_ready_epoch: int = 0,
     max_ctas: int = 0,
     two_cta: bool | int | None = None,
+    out2_multicast: bool = False,
 ) -> torch.Tensor:
     """Launch one batched product on the current CUDA stream.
 
@@ -288,7 +295,9 @@ def gemm(
     dimension is contiguous.  ``out`` (and ``C``) are bf16, fp16 or fp32 of the
     same dtype.  When ``out_ptrs`` (an int64 device tensor with one address per
     batch entry) is given, ``out`` may be ``None`` and each matrix is written to
-    its own allocation (same for ``c_ptrs`` / ``out2_ptrs``).
+    its own allocation (same for ``c_ptrs`` / ``out2_ptrs``).  With
+    ``out2_multicast`` the addresses in ``out2_ptrs`` lie in the NVSwitch multicast
+    mapping of a symmetric buffer and the bf16 copy is stored to every rank at once.
     """
     if A.dim() == 2:
         A = A.unsqueeze(0)
@@ -374,6 +383,10 @@ def gemm(
     elif out2_ptrs is not None:
         args.D2_tab = out2_ptrs.data_ptr()
         args.ldd2 = out2_ld if out2_ld is not None else args.ldd
+    if out2_multicast:
+        # out2 / out2_ptrs are addresses in the multicast mapping of a symmetric buffer
+        assert not symmetric and N % 8 == 0 and int(args.ldd2) % 8 == 0 and (args.D2 or args.D2_tab)
+        args.d2_multimem = 1
     if alpha_vec is not None:
         assert alpha_vec.dtype == torch.float32 and alpha_vec.numel() >= batch
         args.alpha_vec = alpha_vec.data_ptr()

@@ -118,6 +118,17 @@ def _ptr_table(tensors: Sequence[torch.Tensor]) -> torch.Tensor:
     return tab
 
 
+def _addr_table(addrs: Sequence[int], device) -> torch.Tensor:
+    key = tuple(int(a) for a in addrs)
+    tab = _ptr_tables.get(key)
+    if tab is None:
+        if len(_ptr_tables) > 4096:
+            _ptr_tables.clear()
+        tab = torch.tensor(key, dtype=torch.int64).to(device, non_blocking=True)
+        _ptr_tables[key] = tab
+    return tab
+
+
 def _gram(ws: _Workspace, X: torch.Tensor, out: torch.Tensor, left: bool, alpha_vec=None) -> None:
     if left:
         G.gemm(X, X, out, symmetric=True, alpha_vec=alpha_vec)
@@ -155,10 +166,11 @@ def fp16_prescale(m0: int, n0: int) -> float:
     return float(2 ** round(math.log2(math.sqrt(min(m0, n0)))))
 
 
-def _iterate(ws: _Workspace, coefs, restarts, formulation: str, left: bool, xs: _XScale):
+def _iterate(ws: _Workspace, coefs, restarts, formulation: str, left: bool, xs: _XScale, segments=None):
     """Run all products but the final application.  Returns ``(Q, X)``: the
     result is ``Q X_true`` (gram) or ``X`` itself (direct, which needs
-    ``X_stored == X_true``)."""
+    ``X_stored == X_true``).  With a list in ``segments`` (gram only) a copy of
+    the accumulated factor of every restart window is appended to it."""
     X = ws.X
     if formulation == "direct":
         # X <- a X + (b A + c A A) X, A = X X^T
@@ -192,6 +204,8 @@ def _iterate(ws: _Workspace, coefs, restarts, formulation: str, left: bool, xs: 
             _apply(Q, X, left, out=Xn)
             X = Xn
             gram_of(X, R)
+            if segments is not None:
+                segments.append(Q.clone())
             Q = None
         # step polynomial P = c R R + b R + a I
         P = free(Q)
@@ -206,6 +220,8 @@ def _iterate(ws: _Workspace, coefs, restarts, formulation: str, left: bool, xs: 
             G.gemm(R, P, ws.RP, symmetric=True)
             G.gemm(ws.RP, P, Rn, symmetric=True)
             R, Rn = Rn, R
+    if segments is not None:
+        segments.append(Q.clone())
     return Q, X
 
 
@@ -274,6 +290,66 @@ def newton_schulz_batched(
     return out
 
 
+def gram_factors(U: torch.Tensor, coefs, restarts, eps: float = 1e-7):
+    """Left-factor segments of the Gram iteration for ONE matrix, on the kernels.
+
+    Returns ``(segments, transposed, normalizer)`` with the meaning of
+    :func:`dmuon_b200.optim.newton_schulz.gram_newton_schulz_factors`: with
+    ``X`` the matrix oriented wide (transposed when it has more rows than
+    columns) and divided by ``normalizer``, ``segments[-1] @ ... @ segments[0] @ X``
+    is the orthogonalised matrix.  Every segment is a symmetric fp16 matrix of
+    the small dimension.  Because the segments multiply from the left they can
+    be applied to any subset of ``X``'s columns: a tensor-parallel owner sends
+    them instead of the full update (reference dmuon/optim/muon.py:1097-1278,
+    there on library GEMMs)."""
+    assert U.dim() == 2 and U.is_cuda
+    m0, n0 = int(U.shape[0]), int(U.shape[1])
+    ws = workspace(1, m0, n0, torch.float16, U.device)
+    left = m0 <= n0
+    K = fp16_prescale(m0, n0)
+    Uc = U if (U.is_contiguous() and U.dtype in MT._DT) else U.float().contiguous()
+    ws.sumsq.zero_()
+    MT.clip_sumsq([Uc], [0], ws.sumsq)
+    MT.norm_scales(ws.sumsq, ws.scale, ws.scale2, eps)
+    normalizer = 1.0 / ws.scale[0].clone()          # ||U||_F + eps
+    ws.scale.mul_(K)
+    MT.cast([Uc], [ws.X[0]], scale=ws.scale, slots=[0])
+    segs: list[torch.Tensor] = []
+    _iterate(ws, coefs, restarts, "gram", left, _XScale(h=1.0 / K), segments=segs)
+    return [s[0] for s in segs], not left, normalizer
+
+
+def apply_factors(U_local: torch.Tensor, segments, transposed: bool, normalizer: torch.Tensor) -> torch.Tensor:
+    """Apply factor segments from :func:`gram_factors` to this rank's part of
+    the matrix with the tcgen05 GEMM: ``U_local`` is a column block of the wide
+    orientation, i.e. ``[m, n_local]`` when ``transposed`` is false and
+    ``[m_local, n]`` (a row block of the tall matrix) when it is true.  Returns
+    the matching block of the orthogonalised matrix in fp32."""
+    rows, cols = int(U_local.shape[0]), int(U_local.shape[1])
+    d = int(segments[0].shape[-1])
+    assert (cols if transposed else rows) == d
+    K = float(2 ** round(__import__("math").log2(__import__("math").sqrt(d))))
+    scale = (K / normalizer).reshape(1).float()
+    Uc = U_local if (U_local.is_contiguous() and U_local.dtype in MT._DT) else U_local.float().contiguous()
+    X = torch.empty(rows, cols, device=U_local.device, dtype=torch.float16)
+    MT.cast([Uc], [X], scale=scale, slots=[0])
+    last = len(segments) - 1
+    for i, Q in enumerate(segments):
+        out = torch.empty(rows, cols, device=U_local.device, dtype=torch.float32 if i == last else torch.float16)
+        alpha = 1.0 / K if i == last else 1.0
+        if transposed:
+            G.gemm(X, Q, out, alpha=alpha)               # X Q  (Q symmetric)
+        else:
+            G.gemm(Q, X, out, b_mn=True, alpha=alpha)    # Q X
+        X = out
+    return X
+
+
+def factors_supported(rows_local: int, cols_local: int) -> bool:
+    """Operand pitches of the tcgen05 GEMM are multiples of 8 elements."""
+    return rows_local % 8 == 0 and cols_local % 8 == 0
+
+
 def newton_schulz_single(G_in, coefs, restarts, eps, formulation, compute_dtype) -> torch.Tensor:
     shape = G_in.shape
     X = G_in.reshape(1, shape[0], -1)
@@ -301,7 +377,8 @@ def muon_update_batched(
     deltas: Optional[Sequence[torch.Tensor]] = None,
     gscale: Optional[torch.Tensor] = None,
     peer=None,
-) -> None:
+    publish_multicast: Optional[Sequence[int]] = None,
+) -> bool:
     """Momentum, Newton-Schulz and the weight update for ``L`` same-shape
     matrices.
 
@@ -310,10 +387,17 @@ def muon_update_batched(
     a copy of the new weights.  With ``deltas`` instead of ``masters`` the
     pre-scaled update ``-lr*update_scale*NS(u)`` is written there (fp32) and no
     weight is touched (tensor-parallel owners scatter it).
+
+    ``publish_multicast[i]`` (an address in the NVSwitch multicast mapping of the
+    publish arena, same slot as ``publish[i]``) makes the last product store the
+    bf16 copy with ``multimem.st``: every rank's arena receives it.
+
+    Returns whether the bf16 copies were written (by the last product); if not,
+    the caller still has to publish the new master weights.
     """
     L = len(moms)
     if L == 0:
-        return
+        return False
     m0, n0 = int(moms[0].shape[0]), int(moms[0].numel() // moms[0].shape[0])
     dev = moms[0].device
 
@@ -366,9 +450,10 @@ def muon_update_batched(
                     if weight_decay:
                         w.mul_(1.0 - lr * weight_decay)
                     w.add_(O[i], alpha=step_alpha)
-                    if publish is not None and publish[i] is not None:
+                    if publish is not None and publish[i] is not None and publish_multicast is None:
                         publish[i].view(m0, n0).copy_(w)
-        return
+        return deltas is None and publish is not None and publish_multicast is None and all(
+            p is not None for p in publish)
 
     if deltas is not None:
         kw = dict(out_ptrs=_ptr_table(deltas), out_ld=n0, out_dtype=deltas[0].dtype, alpha=step_alpha)
@@ -382,7 +467,12 @@ def muon_update_batched(
             alpha=step_alpha,
             beta=1.0 - float(lr) * float(weight_decay),
         )
-        if publish is not None and all(p is not None for p in publish):
+        if publish_multicast is not None:
+            kw["out2_ptrs"] = _addr_table(publish_multicast, dev)
+            kw["out2_ld"] = n0
+            kw["out2_multicast"] = True
+        elif publish is not None and all(p is not None for p in publish):
             kw["out2_ptrs"] = _ptr_table(publish)
             kw["out2_ld"] = n0
     _run(ws, coefs, restarts, formulation, left, xscale, kw)
+    return "out2_ptrs" in kw

@@ -40,6 +40,13 @@ class _PeerPrologueArgs(ctypes.Structure):
     ]
 
 
+class _MulticastArgs(ctypes.Structure):
+    _fields_ = [
+        ("src", _VP), ("dst", _VP), ("nbytes", _LL), ("n", ctypes.c_int), ("mode", ctypes.c_int),
+        ("dtype", ctypes.c_int), ("blocks_per_tensor", ctypes.c_int),
+    ]
+
+
 class _PullArgs(ctypes.Structure):
     _fields_ = [
         ("src", _VP), ("dst", _VP), ("nbytes", _LL), ("flag_slot", _IA), ("n", ctypes.c_int),
@@ -56,6 +63,7 @@ def _lib():
         ("dmuon_wait_flags", _WaitArgs),
         ("dmuon_peer_prologue", _PeerPrologueArgs),
         ("dmuon_peer_pull", _PullArgs),
+        ("dmuon_multicast_copy", _MulticastArgs),
     ):
         fn = getattr(lib, name)
         fn.argtypes = [ctypes.POINTER(typ), ctypes.c_void_p]
@@ -110,10 +118,14 @@ def copy_async(dst_ptr: int, src_ptr: int, nbytes: int, device: torch.device) ->
 
 def wait_budget_cycles() -> int:
     """Cycle budget of one cross-GPU flag wait (``DMUON_PEER_WAIT_SECONDS``,
-    default 60 s at ~1.9 GHz).  Ranks may legitimately drift apart by seconds
-    (one rank writing a checkpoint, first-step set-up), so the default is far
-    above a step time; tests set it low to exercise the timeout path."""
-    secs = float(os.environ.get("DMUON_PEER_WAIT_SECONDS", "60"))
+    default 20 s at ~1.9 GHz).  Ranks legitimately drift apart by seconds (the
+    first step loads kernels and builds workspaces at different speeds, one
+    rank may be slower through a data loader), so the default is several times
+    the longest wait seen in training and still short for a kernel that only
+    spins; jobs whose ranks stall longer (one rank writing a checkpoint to
+    slow storage inside the step loop) raise it, tests set it to milliseconds
+    to exercise the timeout path."""
+    secs = float(os.environ.get("DMUON_PEER_WAIT_SECONDS", "20"))
     return int(secs * 1.9e9)
 
 
@@ -220,3 +232,32 @@ def peer_pull(
         a.status = status.data_ptr() if status is not None else None
         a.blocks_per_tensor = int(blocks_per_tensor)
         _check(_lib().dmuon_peer_pull(ctypes.byref(a), _stream(device)), "dmuon_peer_pull")
+
+
+def multicast_reduce(mc_srcs: Sequence[int], dsts: Sequence[int], nbytes: Sequence[int], dtype: torch.dtype, device,
+                     blocks_per_tensor: int = 0) -> None:
+    """``dsts[i]`` (local addresses) = element-wise sum over all ranks of the
+    spans at ``mc_srcs[i]`` (addresses in the NVSwitch multicast mapping of a
+    symmetric buffer).  The sum is formed inside the switch
+    (``multimem.ld_reduce``): this rank receives one copy instead of one per
+    peer.  16-bit element types accumulate in fp32 and are rounded once; the
+    summation order is the switch's, not rank order."""
+    _multicast(mc_srcs, dsts, nbytes, 0, dtype, device, blocks_per_tensor)
+
+
+def multicast_broadcast(srcs: Sequence[int], mc_dsts: Sequence[int], nbytes: Sequence[int], device,
+                        blocks_per_tensor: int = 0) -> None:
+    """Store the local spans ``srcs[i]`` to ``mc_dsts[i]`` (multicast
+    addresses): every rank's buffer receives them (``multimem.st``)."""
+    _multicast(srcs, mc_dsts, nbytes, 1, torch.float32, device, blocks_per_tensor)
+
+
+def _multicast(srcs, dsts, nbytes, mode, dtype, device, blocks_per_tensor) -> None:
+    n = len(srcs)
+    for lo, hi in _chunks(n):
+        a = _MulticastArgs()
+        for i in range(lo, hi):
+            k = i - lo
+            a.src[k], a.dst[k], a.nbytes[k] = int(srcs[i]), int(dsts[i]), int(nbytes[i])
+        a.n, a.mode, a.dtype, a.blocks_per_tensor = hi - lo, int(mode), _DT[dtype], int(blocks_per_tensor)
+        _check(_lib().dmuon_multicast_copy(ctypes.byref(a), _stream(device)), "dmuon_multicast_copy")

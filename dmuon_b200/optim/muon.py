@@ -17,19 +17,25 @@ Constructor arguments, per-group keys, group names (``<name>/muon``,
 ``<name>/adamw``) and the update rules follow the reference
 (dmuon/optim/muon.py:127-153, :473-510, :598-638, :1674-1740, :1862-1916).
 
-Scheduling knobs of the reference that are accepted for signature parity but
-have nothing left to schedule here: ``group_prepare_ahead`` (all gradient
-transfers are complete or at least issued when ``step`` starts, and matrices
-are processed by shape, not by group), ``post_step_prefetch_sharded_adamw`` and
+``group_prepare_ahead`` (default on) pipelines the step over blocks of
+communication groups whenever something travels after the update (replicate-axis
+publish, tensor-parallel scatter, DDP broadcast): the next block's gradient
+waits and tensor-parallel gathers are queued before the current block's
+Newton-Schulz products, and each block's publish is dispatched as soon as the
+block is updated (``DMUON_GROUP_PIPELINE_BLOCKS``, default 4; the reference
+pipelines per group, dmuon/optim/muon.py:1446-1546).  Results are bit-identical
+to the unpipelined order.  ``post_step_prefetch_groups``,
+``forward_prefetch_depth``, ``replicate_async`` and the ``tp_distributed_gram*``
+arguments do what their names say.  Accepted for signature parity only:
+``post_step_prefetch_sharded_adamw`` and
 ``sharded_adamw_unshard_separate_stream`` (sharded-AdamW all-gathers share the
-publish lane).  ``post_step_prefetch_groups``, ``forward_prefetch_depth``,
-``replicate_async`` and the ``tp_distributed_gram*`` arguments do what their
-names say.
+publish lane).
 """
 from __future__ import annotations
 
 import logging
 import math
+import os
 import time
 from collections import defaultdict
 from typing import Any, Callable, Optional
@@ -42,7 +48,9 @@ from ..policy import normalize_route
 from ..utils import (
     fence_isolated_process_groups,
     iter_groups,
+    prepare_group_muon_grads,
     prepare_muon_grads,
+    wait_group_muon_grads,
 )
 from .newton_schulz import NewtonSchulz, apply_gram_factors, gram_newton_schulz_factors
 
@@ -434,7 +442,7 @@ class Muon(torch.optim.Optimizer):
             what = "failed" if failed else "queued"
             self._first_step_log(
                 f"first optimizer step {what} after {time.perf_counter() - started:.3f} s of host time"
-                + ("" if failed else "; later steps reuse the workspaces and tile tables built now")
+                + ("" if failed else "; later steps reuse what was set up now")
             )
 
     # ------------------------------------------------------------------ step
@@ -454,14 +462,54 @@ class Muon(torch.optim.Optimizer):
         self._first_step_end(started)
         return loss
 
+    # ------------------------------------------------------------------ group pipeline
+    def _has_post_step_traffic(self, g) -> bool:
+        """Does this group send anything after the update (replicate-axis
+        publish, tensor-parallel scatter, sharded-Muon scatter, DDP broadcast)?"""
+        if getattr(g, "uses_peer_memory", False):
+            return False
+        if g.mode != "fsdp":
+            return True
+        rep = getattr(g, "replicate_group", None)
+        if rep is not None and rep.size() > 1:
+            return True
+        return any(p.tp_group is not None or p._sharded_muon_data is not None for p in g.params)
+
+    def _pipeline_blocks(self) -> list[list]:
+        """Consecutive blocks of communication groups (forward order) that the
+        step works through one after the other: while block *k* runs its
+        Newton-Schulz products, block *k+1*'s gradient waits and tensor-parallel
+        gathers are already queued on the reduce lane and block *k-1*'s post-step
+        publish is in flight on the publish lanes.  The reference pipelines per
+        group (dmuon/optim/muon.py:1446-1546); blocks of several layers keep the
+        per-shape batches large enough for the kernels.  One block (no
+        pipelining) when nothing travels after the update, when
+        ``group_prepare_ahead`` is off, or on the peer-memory plane, where the
+        update kernels themselves publish."""
+        groups = self._comm_groups
+        if not groups or not self.group_prepare_ahead or not any(self._has_post_step_traffic(g) for g in groups):
+            return [list(groups)]
+        try:
+            want = int(os.environ.get("DMUON_GROUP_PIPELINE_BLOCKS", "4"))
+        except ValueError:
+            want = 4
+        n = max(1, min(want, len(groups)))
+        per = (len(groups) + n - 1) // n
+        return [list(groups[i : i + per]) for i in range(0, len(groups), per)]
+
     def _step_impl(self) -> None:
         prof = _StepProfile(self.device, self.record_step_profile)
         groups = self._comm_groups
         gscale, self._pending_gscale = self._pending_gscale, None
 
         rt = getattr(self.comm_ctx, "peer_runtime", None)
+        blocks = self._pipeline_blocks()
         with prof.phase("prepare_muon_grads"):
-            self._ensure_grads_ready()
+            if len(blocks) == 1:
+                self._ensure_grads_ready()
+            else:
+                for g in blocks[0]:
+                    prepare_group_muon_grads(g, use_reduce_lane=True)
             if rt is not None:
                 rt.before_owner_writes()
         # a published copy that survived until here (evaluation forward, no
@@ -472,20 +520,36 @@ class Muon(torch.optim.Optimizer):
             if g.mode == "fsdp":
                 g.stage_publish_targets()
 
-        with prof.phase("muon"):
-            for gi, pg in enumerate(self.param_groups):
-                if pg["use_muon"]:
-                    self._step_muon_bucket(gi, pg, gscale, prof)
-        with prof.phase("dedicated_adamw"):
-            for gi, pg in enumerate(self.param_groups):
-                if not pg["use_muon"]:
-                    self._step_dedicated_adamw(gi, pg, gscale)
+        for bi, block in enumerate(blocks):
+            only = None
+            if len(blocks) > 1:
+                with prof.phase("group_pipeline"):
+                    # queue the next block's waits and gathers before this block's compute is issued
+                    if bi + 1 < len(blocks):
+                        for g in blocks[bi + 1]:
+                            prepare_group_muon_grads(g, use_reduce_lane=True)
+                    for g in block:
+                        wait_group_muon_grads(g)
+                only = {id(p) for g in block for p in g.params}
+            with prof.phase("muon"):
+                for gi, pg in enumerate(self.param_groups):
+                    if pg["use_muon"]:
+                        self._step_muon_bucket(gi, pg, gscale, prof, only)
+            with prof.phase("dedicated_adamw"):
+                for gi, pg in enumerate(self.param_groups):
+                    if not pg["use_muon"]:
+                        self._step_dedicated_adamw(gi, pg, gscale, only)
+            if len(blocks) > 1:
+                with prof.phase("post_step_publish"):
+                    for g in block:
+                        g.post_step_publish_async()
         with prof.phase("post_step_publish"):
             if rt is not None:
                 rt.after_optimizer_consumed()
                 rt.publish_owned()
-            for g in groups:
-                g.post_step_publish_async()
+            if len(blocks) == 1:
+                for g in groups:
+                    g.post_step_publish_async()
             if not self.replicate_async or self._has_tp:
                 for g in groups:
                     g._pre_forward_wait()
@@ -518,16 +582,19 @@ class Muon(torch.optim.Optimizer):
             st["momentum_buffer"] = buf
         return buf
 
-    def _step_muon_bucket(self, gi: int, pg: dict, gscale, prof: _StepProfile) -> None:
+    def _step_muon_bucket(self, gi: int, pg: dict, gscale, prof: _StepProfile, only: Optional[set] = None) -> None:
+        """Muon update of the owned matrices of optimizer group ``gi``; with
+        ``only`` (ids of dedicated parameters) restricted to one pipeline block."""
         lr, mu, wd = float(pg["lr"]), float(pg["momentum"]), float(pg["weight_decay"])
         # every TP peer learns the decay factor locally (the update itself arrives by scatter)
         for dp in self._bucket_all_dps.get(gi, ()):
-            if dp.tp_group is not None:
+            if dp.tp_group is not None and (only is None or id(dp) in only):
                 dp._tp_wd_factor = 1.0 - lr * wd
+        bucket = [dp for dp in self._bucket_dps.get(gi, ()) if only is None or id(dp) in only]
         gram_ids: set[int] = set()
         if self.tp_distributed_gram:
             gram_dps = [
-                dp for dp in self._bucket_dps.get(gi, ())
+                dp for dp in bucket
                 if dp.tp_group is not None and dp._reduced_grad is not None and self._tp_gram_rejection_reason(dp) is None
             ]
             if gram_dps:
@@ -535,7 +602,7 @@ class Muon(torch.optim.Optimizer):
                     self._step_tp_distributed_gram(gram_dps, lr, mu, wd, gscale)
                 gram_ids = {id(dp) for dp in gram_dps}
         work = []
-        for dp in self._bucket_dps.get(gi, ()):
+        for dp in bucket:
             if id(dp) in gram_ids:
                 continue
             if dp.tp_group is not None:
@@ -635,6 +702,9 @@ class Muon(torch.optim.Optimizer):
         for its own shard and applies the factors to it, so the full update is
         never scattered (reference ``dmuon/optim/muon.py:1097-1278``)."""
         nseg, wire = self._tp_gram_segment_count(), self._tp_gram_wire_dtype()
+        on_kernels = self.device.type == "cuda" and _kernels_ok() and not self.ns.deterministic
+        if on_kernels:
+            from ..ops import ns_sm100
         pending = []
         for dp in dps:
             st = self.state[id(dp)]
@@ -660,10 +730,15 @@ class Muon(torch.optim.Optimizer):
                 fbuf = self._momentum_of(dp, (rows, cols), fg.device)
                 fbuf.mul_(mu).add_(fg)
                 full_u = fg.add(fbuf, alpha=mu) if self.nesterov else fbuf
-                segs, tr, norm = gram_newton_schulz_factors(
-                    full_u, steps=self.ns_steps, coefficients=self.ns.coefficients,
-                    restart_iterations=self.ns.restart_iterations, compute_dtype=wire,
-                )
+                if on_kernels:
+                    # every product of the factor computation on the tcgen05 kernels
+                    segs, tr, norm = ns_sm100.gram_factors(
+                        full_u, self.ns.resolved_coefficients(self.ns_steps), self.ns.resolved_restarts())
+                else:
+                    segs, tr, norm = gram_newton_schulz_factors(
+                        full_u, steps=self.ns_steps, coefficients=self.ns.coefficients,
+                        restart_iterations=self.ns.restart_iterations, compute_dtype=wire,
+                    )
                 assert tr == transposed and len(segs) == nseg
                 segs = [s.to(wire).contiguous() for s in segs]
                 norm = norm.reshape(()).float()
@@ -677,7 +752,10 @@ class Muon(torch.optim.Optimizer):
             for s in segs:
                 dist.broadcast(s, src=dp._tp_owner_global_rank, group=dp.tp_group)
         for dp, segs, norm, local_u, transposed, rows, cols in pending:
-            upd = apply_gram_factors(local_u.float(), segs, transposed, norm)
+            if on_kernels and ns_sm100.factors_supported(int(local_u.shape[0]), int(local_u.shape[1])):
+                upd = ns_sm100.apply_factors(local_u, segs, transposed, norm)
+            else:
+                upd = apply_gram_factors(local_u.float(), segs, transposed, norm)
             w = dp._owned_data
             if wd > 0:
                 w.mul_(1.0 - lr * wd)
@@ -695,11 +773,14 @@ class Muon(torch.optim.Optimizer):
             rows = int(shape[0])
             numel = grad.numel() if grad is not None else dp.numel
             gdt = grad.dtype if grad is not None else "peer"
-            key = (rows, numel // rows, gdt, dp._optim_dtype, dp._owned_data.dtype, dp.tp_group is not None)
+            # parameters with and without a publish slot never share a batch: the update kernel writes
+            # the bf16 copies for all matrices of a batch or for none
+            key = (rows, numel // rows, gdt, dp._optim_dtype, dp._owned_data.dtype, dp.tp_group is not None,
+                   getattr(dp, "_publish_view", None) is not None)
             by_shape[key].append((dp, grad))
         coefs = self.ns.resolved_coefficients(self.ns_steps)
         restarts = self.ns.resolved_restarts()
-        for (rows, cols, gdt, _od, _md, is_tp), items in by_shape.items():
+        for (rows, cols, gdt, _od, _md, is_tp, _has_pub), items in by_shape.items():
             cap = ns_sm100.max_batch(rows, cols)
             self._first_step_shape(rows, cols, len(items), "sm_100a kernels, batched by shape")
             for lo in range(0, len(items), cap):
@@ -725,9 +806,19 @@ class Muon(torch.optim.Optimizer):
                 else:
                     masters = [dp._owned_data for dp, _ in chunk]
                     publish = [getattr(dp, "_publish_view", None) for dp, _ in chunk]
-                    ns_sm100.muon_update_batched(grads, moms, masters, publish=publish, **common)
-                    for (dp, _), pub in zip(chunk, publish):
-                        dp._publish_fresh = pub is not None
+                    multicast = None
+                    if rt is not None and rt.copy_mode == "nvls" and all(p is not None for p in publish):
+                        if cols % 8 == 0:
+                            # the last product stores the bf16 weights through the NVSwitch multicast
+                            # mapping of the publish arena: they land on every rank while it runs
+                            esz = rt.pub.element_size()
+                            multicast = [rt.pub_mc + dp._arena_offset * esz for dp, _ in chunk]
+                        else:
+                            publish = [None] * len(chunk)       # published (cast + multicast) after the step
+                    wrote = ns_sm100.muon_update_batched(grads, moms, masters, publish=publish,
+                                                         publish_multicast=multicast, **common)
+                    for dp, _ in chunk:
+                        dp._publish_fresh = bool(wrote)
 
     # ------------------------------------------------------------------ AdamW
     def _adamw_state(self, key, like: torch.Tensor, dtype: torch.dtype) -> dict:
@@ -786,12 +877,13 @@ class Muon(torch.optim.Optimizer):
             if pub is not None:
                 pub.copy_(p)
 
-    def _step_dedicated_adamw(self, gi: int, pg: dict, gscale) -> None:
+    def _step_dedicated_adamw(self, gi: int, pg: dict, gscale, only: Optional[set] = None) -> None:
         entries = []
+        bucket = [dp for dp in self._bucket_dps.get(gi, ()) if only is None or id(dp) in only]
         rt = getattr(self.comm_ctx, "peer_runtime", None)
         if rt is not None:
-            rt.materialize(list(self._bucket_dps.get(gi, ())))
-        for dp in self._bucket_dps.get(gi, ()):
+            rt.materialize(bucket)
+        for dp in bucket:
             if dp._dmuon_route == "sharded_adamw":
                 g, p = dp._sharded_adamw_grad, dp._sharded_adamw_data
             else:
@@ -802,7 +894,7 @@ class Muon(torch.optim.Optimizer):
             st = self._adamw_state(id(dp), p, dp._optim_dtype)
             entries.append((p, g.reshape(p.shape), st, None))
         self._adamw_apply(entries, pg, gscale)
-        for dp in self._bucket_dps.get(gi, ()):
+        for dp in bucket:
             dp._reduced_grad = None
             dp._sharded_adamw_grad = None
 

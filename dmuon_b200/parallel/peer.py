@@ -13,8 +13,15 @@ gradient arena  each rank's local gradients.  Nothing is sent after backward:
                 1/N and applies momentum / Nesterov / cast / Frobenius norm in
                 the same pass.
 
-Bulk data crosses NVLink in one of two ways (``DMUON_PEER_COPY``).  "ce", the
-default: copy-engine transfers.  Readers pull publish spans with asynchronous
+Bulk data crosses NVLink in one of three ways (``DMUON_PEER_COPY``).  "nvls"
+(chosen by "auto", the default, when the symmetric buffers have an NVSwitch
+multicast mapping): the owner's last Newton-Schulz GEMM stores the new bf16
+weights with ``multimem.st``, so they land in every rank's arena while the
+product is still running and readers copy nothing; gradients are summed inside
+the switch -- per layer, during backward, a small kernel on the reduce lane
+reads the owner's span through the multicast mapping with
+``multimem.ld_reduce`` and keeps ONE reduced copy, which the Muon prologue then
+reads locally.  "ce": copy-engine transfers.  Readers pull publish spans with asynchronous
 copies, owners gather the peers' gradient slices of each layer into local
 staging buffers while backward is still running, and the fixed-order fp32 sum
 runs locally inside the Muon prologue; no SM is taken from the forward and
@@ -38,6 +45,7 @@ from typing import Optional
 
 import torch
 import torch.distributed as dist
+from torch.profiler import record_function
 
 from .dgroup import DedicatedParamGroup
 from .dparam import DedicatedParam
@@ -48,6 +56,9 @@ ALIGN = 64          # elements; keeps every slot 128-byte aligned for bf16
 #: CTAs per tensor of the in-backward reduce: enough loads in flight for NVLink
 #: (about 28 KB per CTA) without taking many SMs from the backward GEMMs
 REDUCE_BLOCKS_PER_TENSOR = 24
+#: CTAs of the per-layer in-switch gradient reduce that runs beside the backward GEMMs: each 16-byte
+#: reduce-load returns data already summed over all ranks, so a few CTAs keep up with a layer
+NVLS_REDUCE_BLOCKS = 16
 #: value of the guard words around the arenas in canary mode (exact in bf16, fp16 and fp32)
 CANARY_VALUE = -1.5
 
@@ -81,12 +92,50 @@ def peer_backend_possible(device: torch.device, dp_group, replicate_group, dpara
     return None
 
 
+def peer_backend_possible_from_policies(device, dp_group, replicate_group, params, policies, is_tp) -> Optional[str]:
+    """The same question as :func:`peer_backend_possible`, asked before the
+    dedicated parameters are built (from the resolved per-parameter policies)."""
+    if device.type != "cuda":
+        return "not a CUDA device"
+    if dp_group is None or dp_group.size() < 2:
+        return "single rank"
+    if dp_group.size() > MAX_PEERS:
+        return f"more than {MAX_PEERS} ranks on the shard axis"
+    if replicate_group is not None and replicate_group.size() > 1:
+        return "replicate axis present"
+    if any(is_tp(p) for p in params):
+        return "tensor-parallel parameters"
+    pub, grad = set(), set()
+    for p in params:
+        pol = policies[p]
+        if (pol.route or "") == "sharded_adamw":
+            return "sharded_adamw route"
+        if (pol.muon_forward_unshard or "broadcast") != "broadcast":
+            return "all_gather forward placement"
+        pd = pol.param_dtype or p.dtype
+        pub.add(pd)
+        grad.add(pol.grad_dtype or pd)
+    if len(pub) != 1 or len(grad) != 1:
+        return "mixed publish or gradient dtypes"
+    try:
+        import torch.distributed._symmetric_memory  # noqa: F401
+    except Exception as exc:  # pragma: no cover
+        return f"symmetric memory unavailable: {exc}"
+    return None
+
+
 class PeerSource:
     """What the fused prologue needs to read one batch of gradients."""
 
     def __init__(self, rt: "PeerRuntime", dparams: list[DedicatedParam]):
-        # "ce" copy mode: the peers' slices were gathered into local staging buffers during backward
-        self.peer_bases = rt.stage_bases if rt.copy_mode == "ce" else rt.grad_ptrs
+        if rt.copy_mode == "nvls":
+            # the in-switch sum of all ranks' slices already sits in ONE local buffer
+            self.peer_bases = [rt.reduced_base]
+        elif rt.copy_mode == "ce":
+            # the peers' slices were gathered into local staging buffers during backward
+            self.peer_bases = rt.stage_bases
+        else:
+            self.peer_bases = rt.grad_ptrs
         self.offsets = [p._arena_offset for p in dparams]
         self.numels = [p.numel for p in dparams]
         self.grad_dtype = rt.grad_dtype
@@ -252,11 +301,28 @@ class PeerRuntime:
         # gather of the peers' gradient slices into local staging buffers, the sum then happens locally
         # inside the Muon prologue -- so no SM is taken from the forward / backward GEMMs; "sm" uses the
         # pull / reduce kernels that load through the peer mappings themselves.
-        self.copy_mode = os.environ.get("DMUON_PEER_COPY", "ce").strip().lower()
-        if self.copy_mode not in ("ce", "sm"):
-            raise ValueError("DMUON_PEER_COPY must be 'ce' or 'sm'")
+        self.pub_mc = int(getattr(self.pub_hdl, "multicast_ptr", 0) or 0)
+        self.grad_mc = int(getattr(self.grad_hdl, "multicast_ptr", 0) or 0)
+        self.copy_mode = os.environ.get("DMUON_PEER_COPY", "auto").strip().lower()
+        if self.copy_mode not in ("auto", "nvls", "ce", "sm"):
+            raise ValueError("DMUON_PEER_COPY must be 'auto', 'nvls', 'ce' or 'sm'")
         if self.fused_forward:
             self.copy_mode = "sm"       # the fused forward kernels do their own fetching
+        if self.copy_mode in ("auto", "nvls"):
+            # every rank must take the same decision: all need a multicast mapping of both arenas
+            ok = torch.tensor(
+                [int(self.pub_mc != 0 and self.grad_mc != 0 and self.pub.element_size() == 2)], device=self.device
+            )
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=dp_group)
+            if bool(ok.item()):
+                self.copy_mode = "nvls"
+            elif self.copy_mode == "nvls":
+                raise RuntimeError(
+                    "DMUON_PEER_COPY=nvls: the symmetric arenas have no NVSwitch multicast mapping on every rank "
+                    "(or the published dtype is not 16-bit)"
+                )
+            else:
+                self.copy_mode = "ce"
         for g in groups:
             g._span_by_owner = {}
             for s_, plist in g._pub_by_shard.items():
@@ -268,6 +334,15 @@ class PeerRuntime:
         self.own_hi = max((hi for _, hi in mine), default=0)
         self.stage = None
         self.stage_bases = list(self.grad_ptrs)
+        self.reduced = None
+        self.reduced_base = 0
+        self._consumed_signalled_epoch = 0
+        self._ready_waited_epoch = 0
+        if self.copy_mode == "nvls":
+            span = max(self.own_hi - self.own_lo, ALIGN)
+            self.reduced = torch.zeros(span, dtype=self.grad_dtype, device=self.device)
+            # address of arena offset 0 in the reduced copy (only [own_lo, own_hi) is backed)
+            self.reduced_base = self.reduced.data_ptr() - self.own_lo * self.grad.element_size()
         if self.copy_mode == "ce" and self.own_hi > self.own_lo and self.world > 1:
             span = self.own_hi - self.own_lo
             self.stage = torch.empty((self.world - 1) * span, dtype=self.grad_dtype, device=self.device)
@@ -379,6 +454,17 @@ class PeerRuntime:
     # ------------------------------------------------------------------ publish side
     def before_owner_writes(self) -> None:
         """Queue the wait that protects readers still pulling the current epoch."""
+        with record_function(f"dmuon.peer.before_owner_writes.epoch{self.pub_epoch}"):
+            self._before_owner_writes()
+
+    def _before_owner_writes(self) -> None:
+        if self.copy_mode == "nvls":
+            # Owners store straight into every rank's arena, so "consumed" means: this rank has
+            # finished every forward / backward that reads the current weights.  That is true at
+            # this point of the current stream (the optimizer step or a checkpoint load follows).
+            self._acknowledge_epoch()
+            self._wait_all(KIND_PUB_CONSUMED, self.pub_epoch)
+            return
         # a group whose forward did not run this epoch still has to acknowledge it
         lane = self.ctx.broadcast_lane
         pending = [g for g in self.groups if g._pulled_epoch != self.pub_epoch]
@@ -388,14 +474,30 @@ class PeerRuntime:
                 for g in pending:
                     self.pull_group(g)
             lane.mark().wait_on_current()
+        if self.fused_forward:
+            # fused linears acknowledge from announce_grads(), which needs a backward; without one in
+            # this epoch (checkpoint load right after construction, evaluation only) do it here, after
+            # the pulls queued above
+            self._acknowledge_epoch()
         if self.pub_epoch > 0:
             self._wait_all(KIND_PUB_CONSUMED, self.pub_epoch)
+
+    def _acknowledge_epoch(self) -> None:
+        """Tell every owner, once per publish epoch, that this rank no longer
+        needs the epoch's weights to stay as they are (stream-ordered)."""
+        if self._consumed_signalled_epoch != self.pub_epoch:
+            self._signal(KIND_PUB_CONSUMED, self.pub_epoch)
+            self._consumed_signalled_epoch = self.pub_epoch
 
     def publish_owned(self) -> None:
         """Bring the owner's publish slots up to date and announce the new epoch."""
         from ..ops import multi_tensor as MT
 
         stale = [p for g in self.groups for p in g.bcast_params if p.is_owner and not p._publish_fresh]
+        with record_function(f"dmuon.peer.publish_owned.{self.copy_mode}.epoch{self.pub_epoch + 1}.stale{len(stale)}"):
+            self._publish_owned(stale, MT)
+
+    def _publish_owned(self, stale, MT) -> None:
         if stale:
             srcs = [p._owned_data.reshape(-1) for p in stale]
             dsts = [p._publish_view.reshape(-1) for p in stale]
@@ -404,6 +506,17 @@ class PeerRuntime:
                     MT.cast(srcs, dsts)
                 else:
                     torch._foreach_copy_(dsts, srcs)
+                if self.copy_mode == "nvls":
+                    # slots the update kernel did not multicast itself (AdamW-routed tensors, the first
+                    # publish, a checkpoint load): replicate the local copy to every rank's arena
+                    from ..ops import peer as P
+
+                    esz = self.pub.element_size()
+                    spans = [(p._arena_offset * esz, (p.numel + ALIGN - 1) // ALIGN * ALIGN * esz) for p in stale]
+                    P.multicast_broadcast(
+                        [self.pub.data_ptr() + off for off, _ in spans], [self.pub_mc + off for off, _ in spans],
+                        [nb for _, nb in spans], self.device,
+                    )
         for g in self.groups:
             for p in g.bcast_params:
                 p._publish_fresh = False
@@ -412,15 +525,27 @@ class PeerRuntime:
         self._pulled_groups = 0
         for g in self.groups:
             g._pulled_epoch = -1
-        if self._remote_groups == 0:
+        if self._remote_groups == 0 and self.copy_mode != "nvls":
             # this rank reads nothing from anybody: acknowledge right away
-            self._signal(KIND_PUB_CONSUMED, self.pub_epoch)
+            self._acknowledge_epoch()
 
     def pull_group(self, g: "PeerParamGroup") -> None:
         """Copy this group's slots from their owners into the local arena."""
+        if g._pulled_epoch == self.pub_epoch:
+            return
+        with record_function(f"dmuon.peer.unshard.{self.copy_mode}.{g.name}"):
+            self._pull_group(g)
+
+    def _pull_group(self, g: "PeerParamGroup") -> None:
         from ..ops import peer as P
 
-        if g._pulled_epoch == self.pub_epoch:
+        if self.copy_mode == "nvls":
+            # the owners' stores already put the weights here: only wait (once per epoch and lane)
+            # until every owner has announced the epoch
+            if self._ready_waited_epoch != self.pub_epoch:
+                P.wait_flags(self.flags, KIND_PUB_READY * MAX_PEERS, self.world, self.pub_epoch, self.status)
+                self._ready_waited_epoch = self.pub_epoch
+            g._pulled_epoch = self.pub_epoch
             return
         remote = [p for s, plist in g._pub_by_shard.items() if s != self.rank for p in plist]
         if remote:
@@ -428,7 +553,7 @@ class PeerRuntime:
             self.pull_params([p for p in remote if not getattr(p, "_fused_linear", False)])
             self._pulled_groups += 1
             if self._pulled_groups == self._remote_groups and not self.fused_forward:
-                self._signal(KIND_PUB_CONSUMED, self.pub_epoch)
+                self._acknowledge_epoch()
         g._pulled_epoch = self.pub_epoch
 
     def pull_params(self, plist: list[DedicatedParam]) -> None:
@@ -478,7 +603,7 @@ class PeerRuntime:
             if self.fused_forward and self._remote_groups > 0:
                 # fused linears pull on the compute stream during forward; this point
                 # is stream-ordered after all of them
-                self._signal(KIND_PUB_CONSUMED, self.pub_epoch)
+                self._acknowledge_epoch()
 
     # per-group reduce that overlaps with the rest of backward ("backward" mode)
     def signal_group_packed(self, g: "PeerParamGroup", count: int) -> None:
@@ -489,9 +614,24 @@ class PeerRuntime:
     def launch_group_reduce(self, g: "PeerParamGroup", owned: list[DedicatedParam], count: int):
         """Queue, on the reduce lane, the kernel that sums this group's owned
         gradients over all ranks' arenas as soon as every rank has packed them."""
+        with record_function(f"dmuon.peer.reduce.{self.copy_mode}.{g.name}.params{len(owned)}"):
+            return self._launch_group_reduce(g, owned, count)
+
+    def _launch_group_reduce(self, g: "PeerParamGroup", owned: list[DedicatedParam], count: int):
         from ..ops import peer as P
 
         lane = self.ctx.reduce_lane
+        if self.copy_mode == "nvls":
+            # one reduce-load per 16 bytes returns the sum over ALL ranks' arenas, formed in the switch:
+            # the owner ingests its span once, not once per peer, and keeps a single reduced copy
+            lo, hi = g._span_by_owner[self.rank]
+            gsz = self.grad.element_size()
+            lane.follow_current()
+            with lane.use():
+                P.wait_flags(self.flags, (4 + g._group_index) * MAX_PEERS, self.world, count, self.status)
+                P.multicast_reduce([self.grad_mc + lo * gsz], [self.reduced_base + lo * gsz], [(hi - lo) * gsz],
+                                   self.grad_dtype, self.device, blocks_per_tensor=NVLS_REDUCE_BLOCKS)
+            return lane.mark()
         if self.copy_mode == "ce":
             # gather instead of reduce: bring every peer's slice of this group's owned span into the
             # local staging buffers with copy-engine transfers; the Muon prologue sums them later
@@ -528,6 +668,12 @@ class PeerRuntime:
         todo = [p for p in dparams if p.is_owner and p._peer_grad_pending and p._reduced_grad is None]
         if not todo:
             return
+        with record_function(f"dmuon.peer.materialize_reduced_grads.params{len(todo)}"):
+            self._materialize(todo)
+
+    def _materialize(self, todo: list[DedicatedParam]) -> None:
+        from ..ops import peer as P
+
         outs = [torch.empty(p._orig_size, dtype=torch.float32, device=self.device) for p in todo]
         src = self.source_for(todo)
         P.peer_prologue(src.peer_bases, src.offsets, src.numels, src.grad_dtype, [None] * len(todo),
@@ -612,7 +758,7 @@ class PeerParamGroup(DedicatedParamGroup):
         rt = self.runtime
         for p in direct:
             p._grad_in_arena = False
-        with torch.no_grad():
+        with torch.no_grad(), record_function(f"dmuon.peer.pack_grads.{self.name}.copied{len(with_grad)}.direct{len(direct)}"):
             rt.before_pack()
             dsts = [p._grad_view for p, _ in with_grad]
             srcs = [g for _, g in with_grad]
@@ -626,7 +772,7 @@ class PeerParamGroup(DedicatedParamGroup):
                 p._peer_grad_pending = True
                 p.clear_local_grad()
         self._packed_this_step = True
-        if (rt.reduce_mode == "backward" or rt.copy_mode == "ce") and not self._no_sync:
+        if (rt.reduce_mode == "backward" or rt.copy_mode in ("ce", "nvls")) and not self._no_sync:
             # tell every rank this group's running sum is in the arena, then (as an
             # owner) reduce it on the side lane while backward continues.  A later
             # micro-batch repeats this and overwrites the result with the larger sum.
@@ -636,8 +782,9 @@ class PeerParamGroup(DedicatedParamGroup):
             owned = [p for p, _ in with_grad if p.is_owner] + [p for p in direct if p.is_owner and id(p) not in seen]
             if owned:
                 self._reduce_ticket = rt.launch_group_reduce(self, owned, self._pack_count)
-                # after a copy-engine gather the sum is still to be done (inside the Muon prologue)
-                self._reduce_owned = owned if rt.copy_mode != "ce" else []
+                # after a copy-engine gather the sum is still to be done (inside the Muon prologue); after
+                # an in-switch reduce the scale, momentum and cast are
+                self._reduce_owned = owned if rt.copy_mode == "sm" else []
 
     def has_pending_reduce(self) -> bool:
         if self._reduce_ticket is not None:

@@ -127,3 +127,44 @@ def test_replicate_axis_reduce_can_be_delayed_to_the_optimizer():
     for r in range(4):
         for n, t in now[r][0].items():
             assert torch.equal(t, later[r][0][n]), (r, n)
+
+
+def _body_pipeline(rank, world, mode, prepare_ahead):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+
+    model = _build_model()
+    if mode == "hsdp":
+        mesh = init_device_mesh("cpu", (2, world // 2), mesh_dim_names=("replicate", "shard"))
+        dmuon.dedicate_params(model, mesh["shard"], _pred, reshard_after_forward=False, replicate_mesh=mesh["replicate"])
+        for layer in model.layers:
+            fully_shard(layer, mesh=mesh)
+        fully_shard(model, mesh=mesh)
+    else:
+        mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("dp",))
+        dmuon.dedicate_params_ddp(model, mesh, _pred)
+        dmuon.replicate(model, mesh)
+    opt = dmuon.Muon(model, lr=HP["lr"], adamw_lr=HP["adamw_lr"], weight_decay=HP["weight_decay"],
+                     momentum=HP["momentum"], group_prepare_ahead=prepare_ahead, record_step_profile=True,
+                     first_step_progress_log=False)
+    blocks = len(opt._pipeline_blocks())
+    _train(model, opt, rank, world, 3)
+    prof = opt.consume_last_step_profile()
+    dmuon.wait_all_replicate_broadcasts(model)
+    return dmuon.get_model_state_dict(model, rank0_only=False), blocks, sorted(prof)
+
+
+@pytest.mark.parametrize("mode", ["hsdp", "ddp"])
+def test_group_pipeline_is_bit_identical_to_the_unpipelined_step(mode):
+    """``group_prepare_ahead``: the step walks through blocks of groups (next
+    block's gradient waits queued ahead, each block's publish dispatched right
+    after its update) and must produce exactly the weights of the one-block step."""
+    piped = run_ranks(_body_pipeline, 4, args=(mode, True))
+    plain = run_ranks(_body_pipeline, 4, args=(mode, False))
+    assert all(r[1] == 4 for r in piped) and all(r[1] == 1 for r in plain)      # 4 layers -> 4 blocks vs one
+    assert "group_pipeline_ms" in piped[0][2] and "group_pipeline_ms" not in plain[0][2]
+    for r in range(4):
+        for n, t in piped[r][0].items():
+            assert torch.equal(t, plain[r][0][n]), (mode, r, n)

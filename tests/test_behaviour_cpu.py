@@ -239,3 +239,52 @@ def test_three_dimensional_weights_are_orthogonalised_as_matrices():
         assert abs(a - b) < 1e-4 * max(1.0, abs(b)), (losses, ref_losses)
     for n, p in ref.named_parameters():
         assert sd[n].shape == p.shape and (sd[n] - p).abs().max().item() < 2e-4, n
+
+
+class _WithBuffer(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.a_proj = nn.Linear(16, 32, bias=False)
+        self.b_proj = nn.Linear(32, 16, bias=False)
+        self.norm = nn.LayerNorm(16)
+        self.register_buffer("running", torch.zeros(16))
+
+    def forward(self, x):
+        return self.norm(self.b_proj(torch.relu(self.a_proj(x))) + self.running)
+
+
+def _bcast_load_body(rank, world):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+
+    torch.manual_seed(0)
+    model = _WithBuffer()
+    mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("dp",))
+    dmuon.dedicate_params(model, mesh, lambda n, p: "proj" in n and p.ndim == 2)
+    fully_shard(model, mesh=mesh)
+    # only rank 0 holds data; one parameter is absent from the file
+    sd = {}
+    if rank == 0:
+        g = torch.Generator().manual_seed(9)
+        sd = {"a_proj.weight": torch.randn(32, 16, generator=g), "norm.weight": torch.full((16,), 3.0),
+              "norm.bias": torch.full((16,), -1.0), "running": torch.arange(16.0)}
+    dmuon.set_model_state_dict(model, sd, strict=False, broadcast_from_rank0=True)
+    out = dmuon.get_model_state_dict(model, rank0_only=False)
+    return {k: v.clone() for k, v in out.items()}, model.running.clone()
+
+
+def test_broadcast_load_carries_buffers_and_skips_missing_keys_on_every_rank():
+    """``broadcast_from_rank0``: buffers travel like parameters, and a key that
+    rank 0 does not have is skipped by ALL ranks (nobody waits in a broadcast
+    that rank 0 never enters)."""
+    res = run_ranks(_bcast_load_body, 2, timeout=120)
+    g = torch.Generator().manual_seed(9)
+    want_a = torch.randn(32, 16, generator=g)
+    for sd, running in res:
+        assert torch.equal(sd["a_proj.weight"], want_a)
+        assert torch.equal(sd["norm.weight"], torch.full((16,), 3.0))
+        assert torch.equal(running, torch.arange(16.0))
+    # the absent matrix kept its initial value, identically on both ranks
+    assert torch.equal(res[0][0]["b_proj.weight"], res[1][0]["b_proj.weight"])

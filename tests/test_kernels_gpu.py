@@ -360,3 +360,34 @@ def test_newton_schulz_graph_replay_matches_eager(monkeypatch):
         orth_b = ((b.float() @ b.float().T - eye).norm() / 384 ** 0.5).item()
         assert rel < 2e-2 and abs(orth_a - orth_b) < 0.01, (rel, spread, orth_a, orth_b)
     assert dmuon.get_backend_status()["cuda_graph_replay"] is True
+
+
+@pytest.mark.parametrize("shape", [(512, 1536), (1536, 512)])
+def test_gram_factors_on_kernels_reproduce_newton_schulz(shape):
+    """The factor segments the tensor-parallel owner sends (computed on the
+    tcgen05 GEMM) applied to column blocks of the matrix (again on the GEMM)
+    give the same result as orthogonalising the whole matrix in fp32."""
+    from dmuon_b200.ops import gemm as G
+    from dmuon_b200.ops import ns_sm100
+    from dmuon_b200.optim.newton_schulz import (
+        DEFAULT_COEFFICIENTS, DEFAULT_RESTART_ITERATIONS, apply_gram_factors, gram_newton_schulz_factors)
+
+    dev = _dev()
+    torch.manual_seed(5)
+    U = torch.randn(*shape, device=dev)
+    segs, transposed, norm = ns_sm100.gram_factors(U, DEFAULT_COEFFICIENTS, DEFAULT_RESTART_ITERATIONS)
+    assert transposed == (shape[0] > shape[1]) and len(segs) == 2
+    assert all(s.dtype == torch.float16 and s.shape == (512, 512) for s in segs)
+    # fp32 PyTorch reference of the same schedule
+    rsegs, rtr, rnorm = gram_newton_schulz_factors(U, compute_dtype=torch.float32, deterministic=True)
+    assert rtr == transposed
+    assert abs(float(norm) - float(rnorm)) < 1e-3 * float(rnorm)
+    ref = apply_gram_factors(U, rsegs, rtr, rnorm)
+    # apply to two halves along the dimension a tensor-parallel group would shard
+    halves = U.chunk(2, dim=0 if transposed else 1)
+    got = torch.cat([ns_sm100.apply_factors(h.contiguous(), segs, transposed, norm) for h in halves],
+                    dim=0 if transposed else 1)
+    torch.cuda.synchronize()
+    G.check_status(dev)
+    assert got.dtype == torch.float32 and got.shape == U.shape
+    assert (got - ref).abs().max().item() < 2e-2 * ref.abs().max().item()

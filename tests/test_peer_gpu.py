@@ -138,6 +138,10 @@ def _train_body(rank, world, backend, steps):
         backend = "peer"
     if backend == "peer-optimizer-reduce":
         os.environ["DMUON_PEER_REDUCE"] = "optimizer"
+        os.environ["DMUON_PEER_COPY"] = "ce"
+        backend = "peer"
+    if backend in ("peer-ce", "peer-nvls"):
+        os.environ["DMUON_PEER_COPY"] = backend[5:]
         backend = "peer"
     dev = torch.device("cuda", rank)
     cfg = LlamaConfig(vocab_size=2048, d_model=512, n_layers=3, n_heads=8, n_kv_heads=4, head_dim=64,
@@ -198,8 +202,15 @@ def test_peer_data_plane_matches_nccl():
     world = 2
     steps = 4
     ref = run_ranks(_train_body, world, args=("nccl", steps), backend="nccl", timeout=600)
-    got = run_ranks(_train_body, world, args=("peer", steps), backend="nccl", timeout=600)
+    got = run_ranks(_train_body, world, args=("peer-ce", steps), backend="nccl", timeout=600)
     alt = run_ranks(_train_body, world, args=("peer-optimizer-reduce", steps), backend="nccl", timeout=600)
+    nvls = run_ranks(_train_body, world, args=("peer-nvls", steps), backend="nccl", timeout=600)
+    assert nvls[0][2] and nvls[0][3] == 21
+    for a, b in zip(nvls[0][0], ref[0][0]):
+        assert abs(a - b) < 2e-2 * max(1.0, abs(b)), (nvls[0][0], ref[0][0])
+    for k, v in ref[0][1].items():
+        rel = (nvls[0][1][k].float() - v.float()).norm().item() / (v.float().norm().item() + 1e-12)
+        assert rel < 0.15, (k, rel)
     flat = run_ranks(_train_body, world, args=("hsdp-flat", steps), backend="nccl", timeout=600)
     assert flat[0][2] and flat[0][3] == 21
     for a, b in zip(flat[0][0], ref[0][0]):
@@ -293,15 +304,19 @@ def _reduce_check_body(rank, world, fused=False, reduce_mode="backward", copy_mo
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 @pytest.mark.parametrize(
     "fused,reduce_mode,copy_mode",
-    [(False, "backward", "ce"), (False, "optimizer", "ce"), (False, "backward", "sm"), (False, "optimizer", "sm"),
-     (True, "backward", "sm")],
+    [(False, "backward", "nvls"), (False, "backward", "ce"), (False, "optimizer", "ce"), (False, "backward", "sm"),
+     (False, "optimizer", "sm"), (True, "backward", "sm")],
 )
 def test_peer_reduce_and_publish_are_exact(fused, reduce_mode, copy_mode):
     """Copy-engine transfers + local sum ("ce") and the kernels that load through the
-    peer mappings ("sm") must both deliver exactly the mean gradient and the owner's weights."""
-    world = min(4, torch.cuda.device_count())
+    peer mappings ("sm") must both deliver exactly the mean gradient and the owner's weights.
+    The NVSwitch form ("nvls") publishes exactly as well (the update kernel's multicast
+    store carries the same bf16 values); its gradient sum is formed in the switch with fp32
+    accumulation and rounded once to the bf16 gradient type, so it is within one bf16
+    rounding of the exact mean, in the switch's order rather than rank order."""
+    world = min(8, torch.cuda.device_count())
     worst = run_ranks(_reduce_check_body, world, args=(fused, reduce_mode, copy_mode), backend="nccl", timeout=600)
-    assert max(worst) < 1e-5, worst
+    assert max(worst) < (1e-5 if copy_mode != "nvls" else 6e-3), worst
 
 
 def _scalar_body(rank, world):
@@ -336,12 +351,18 @@ def _scalar_body(rank, world):
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_in_kernel_scalar_allreduce_matches_nccl():
-    world = min(4, torch.cuda.device_count())
+    world = min(8, torch.cuda.device_count())
     worst = run_ranks(_scalar_body, world, backend="nccl", timeout=300)
     assert max(worst) < 1e-5, worst
 
 
-def _ckpt_body(rank, world):
+def _ckpt_body(rank, world, plane="auto"):
+    import os
+
+    if plane == "fused":
+        os.environ["DMUON_FUSED_PUBLISH"] = "1"
+    else:
+        os.environ["DMUON_PEER_COPY"] = plane
     from torch.distributed.device_mesh import init_device_mesh
     from torch.distributed.fsdp import fully_shard
 
@@ -371,6 +392,13 @@ def _ckpt_body(rank, world):
         with torch.no_grad():
             return float(model(ids[:, :-1], labels=ids[:, 1:]))
 
+    # a load before any step (the usual resume) and one after an evaluation-only forward: neither epoch
+    # saw a backward, so the owners' "everybody is done with the old weights" wait must not depend on one
+    initial = dmuon.get_model_state_dict(model, rank0_only=False)
+    dmuon.set_model_state_dict(model, initial)
+    first = evaluate()
+    dmuon.set_model_state_dict(model, initial)
+    assert evaluate() == first
     step()
     saved = dmuon.get_model_state_dict(model, rank0_only=False)
     at_save = evaluate()
@@ -384,7 +412,132 @@ def _ckpt_body(rank, world):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_loading_a_state_dict_republishes_on_the_peer_plane():
-    for at_save, moved, restored in run_ranks(_ckpt_body, 2, backend="nccl", timeout=300):
+@pytest.mark.parametrize("plane", ["auto", "ce", "fused"])
+def test_loading_a_state_dict_republishes_on_the_peer_plane(plane):
+    for at_save, moved, restored in run_ranks(_ckpt_body, 2, args=(plane,), backend="nccl", timeout=300):
         assert abs(moved - at_save) > 1e-3          # training did change the weights
         assert restored == at_save                  # and every rank reads the restored ones again
+
+
+def _accum_body(rank, world, use_no_sync, plane):
+    import contextlib
+    import os
+
+    os.environ["DMUON_PEER_COPY"] = plane
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+    from dmuon_b200.models.llama import LlamaConfig, LlamaModel
+
+    dev = torch.device("cuda", rank)
+    cfg = LlamaConfig(vocab_size=256, d_model=128, n_layers=2, n_heads=2, n_kv_heads=2, head_dim=64,
+                      ffn_hidden=256, rope_theta=10000.0)
+    torch.manual_seed(0)
+    with torch.device(dev):
+        model = LlamaModel(cfg)
+    mesh = init_device_mesh("cuda", (world,), mesh_dim_names=("dp",))
+    dmuon.dedicate_params(model, mesh, lambda n, p: "proj" in n and p.ndim == 2, comm_backend="peer",
+                          param_policy={"defaults": {"param_dtype": "bf16", "grad_dtype": "fp32"}})
+    for layer in model.layers:
+        fully_shard(layer, mesh=mesh)
+    fully_shard(model, mesh=mesh)
+    opt = dmuon.Muon(model, lr=0.02)
+    g = torch.Generator().manual_seed(50 + rank)
+    for _ in range(2):
+        ids = torch.randint(0, cfg.vocab_size, (4, 65), generator=g).to(dev)
+        opt.zero_grad()
+        hold = dmuon.no_sync(model) if use_no_sync else contextlib.nullcontext()
+        with hold:      # first micro-batch: with no_sync nothing is announced to the owners yet
+            (model(ids[:2, :-1], labels=ids[:2, 1:]) / 2).backward()
+        (model(ids[2:, :-1], labels=ids[2:, 1:]) / 2).backward()
+        opt.step()
+    model._dedicated_comm_ctx.peer_runtime.check()
+    sd = dmuon.get_model_state_dict(model, rank0_only=False)
+    return {k: v for k, v in sd.items() if "proj" in k}
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("plane", ["auto", "ce"])
+def test_no_sync_accumulation_on_the_peer_plane(plane):
+    """Two micro-batches per step: accumulating the first one locally under
+    ``no_sync`` gives the weights that two synchronised backward passes give
+    (the reference's criterion is 1e-2 max abs, tests/distributed/test_grad_accum.py:226-229)."""
+    a = run_ranks(_accum_body, 2, args=(False, plane), backend="nccl", timeout=300)
+    b = run_ranks(_accum_body, 2, args=(True, plane), backend="nccl", timeout=300)
+    for k, v in a[0].items():
+        assert (b[0][k].float() - v.float()).abs().max().item() < 1e-2, k
+        assert torch.equal(b[0][k], b[1][k])
+
+
+def _ddp_peer_body(rank, world, plane):
+    import os
+
+    import torch.distributed as dist
+
+    os.environ["DMUON_PEER_COPY"] = plane
+    from torch.distributed.device_mesh import init_device_mesh
+
+    import dmuon_b200 as dmuon
+    from dmuon_b200.models.llama import LlamaConfig, LlamaModel
+
+    dev = torch.device("cuda", rank)
+    cfg = LlamaConfig(vocab_size=512, d_model=256, n_layers=2, n_heads=4, n_kv_heads=4, head_dim=64,
+                      ffn_hidden=512, rope_theta=10000.0)
+    torch.manual_seed(0)
+    with torch.device(dev):
+        model = LlamaModel(cfg).bfloat16()
+    mesh = init_device_mesh("cuda", (world,), mesh_dim_names=("dp",))
+    dmuon.dedicate_params_ddp(model, mesh, lambda n, p: "proj" in n and p.ndim == 2, comm_backend="peer")
+    dmuon.replicate(model, mesh)
+    ctx = model._dedicated_comm_ctx
+    assert ctx.ddp_on_peer_plane and ctx.peer_runtime is not None and ctx.mode == "ddp"
+    assert ctx.peer_runtime.copy_mode == plane
+    opt = dmuon.Muon(model, lr=0.02)
+    worst, losses = 0.0, []
+    for step in range(3):
+        g = torch.Generator().manual_seed(7 + rank + 10 * step)
+        ids = torch.randint(0, cfg.vocab_size, (2, 65), generator=g).to(dev)
+        opt.zero_grad()
+        loss = model(ids[:, :-1], labels=ids[:, 1:])
+        loss.backward()
+        want = {}
+        for dp in dmuon.get_dedicated_params(model):
+            t = dp._grad_view.float().clone()
+            dist.all_reduce(t)
+            want[dp.fqn] = t / world
+        opt._ensure_grads_ready(materialize=True)
+        for dp in dmuon.get_owned_params(model):
+            worst = max(worst, (dp._reduced_grad - want[dp.fqn]).abs().max().item() / (want[dp.fqn].abs().max().item() + 1e-12))
+        opt.step()
+        lt = loss.detach().float().clone()
+        dist.all_reduce(lt)
+        losses.append(float(lt) / world)
+        model(ids[:, :-1])
+        torch.cuda.synchronize()
+        for dp in dmuon.get_dedicated_params(model):
+            ref = dp._owned_data.to(torch.bfloat16) if dp.is_owner else torch.empty(dp._orig_size, dtype=torch.bfloat16, device=dev)
+            dist.broadcast(ref, src=dp.owner_shard)
+            assert torch.equal(dp._unsharded_param.data, ref), dp.fqn
+    # the replicated (non-dedicated) parameters stay identical across ranks
+    for n, p in model.named_parameters():
+        if "proj" not in n:
+            q = p.detach().float().clone()
+            dist.broadcast(q, src=0)
+            assert torch.equal(q, p.detach().float()), n
+    ctx.peer_runtime.check()
+    return worst, losses
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("plane", ["nvls", "ce"])
+def test_replicated_placement_runs_on_the_peer_plane(plane):
+    """``dedicate_params_ddp`` + ``replicate`` on one NVSwitch domain: the
+    dedicated matrices are reduced out of the ranks' gradient arenas and the
+    owner's update reaches every rank's copy (no NCCL reduce / fp32 broadcast);
+    the mean gradient and the published weights are checked against collectives."""
+    world = min(4, torch.cuda.device_count())
+    res = run_ranks(_ddp_peer_body, world, args=(plane,), backend="nccl", timeout=600)
+    assert max(r[0] for r in res) < (1e-5 if plane == "ce" else 6e-3)
+    losses = res[0][1]
+    assert losses[-1] < losses[0]

@@ -213,7 +213,9 @@ def _plane_name(ctx) -> str:
     if rt is None:
         return "nccl"
     if rt.copy_mode == "nvls":
-        return ("NVSwitch multicast: weights stored to all ranks by the update GEMM's epilogue (multimem.st), "
+        how = ("by the update GEMM's epilogue" if rt.nvls_publish == "epilogue"
+               else "by a copy kernel on the publish lane while the next Newton-Schulz batch runs")
+        return (f"NVSwitch multicast: weights stored to all ranks {how} (multimem.st), "
                 "gradients summed in the switch per layer during backward (multimem.ld_reduce)")
     if rt.copy_mode == "ce":
         return "peer memory: copy-engine pulls and gradient gather, sum fused into the Muon prologue kernel"

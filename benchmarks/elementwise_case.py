@@ -8,7 +8,11 @@ root when present, otherwise the value passed with --peak-gbs).
     python benchmarks/elementwise_case.py --op xent --rows 2048
     python benchmarks/elementwise_case.py --op prologue
 
-Ops: swiglu_fwd, swiglu_bwd, rope, xent, prologue, adamw, clip_sumsq.
+Ops: swiglu_fwd, swiglu_bwd, rope, xent, prologue, adamw, clip_sumsq, clip_scale,
+cast, peer_prologue, peer_pull, tp_gather, tp_apply.  The peer and
+tensor-parallel kernels run on ONE device here: the buffers of the "other
+ranks" are other allocations of the same GPU, which exercises the same code
+and gives the HBM-side rate (the NVLink-side rate is in bench_comm.py).
 """
 from __future__ import annotations
 
@@ -33,7 +37,8 @@ def peak_gbs(default: float) -> tuple[float, str]:
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", required=True,
-                    choices=("swiglu_fwd", "swiglu_bwd", "rope", "xent", "prologue", "adamw", "clip_sumsq"))
+                    choices=("swiglu_fwd", "swiglu_bwd", "rope", "xent", "prologue", "adamw", "clip_sumsq", "clip_scale",
+                             "cast", "peer_prologue", "peer_pull", "tp_gather", "tp_apply"))
     ap.add_argument("--rows", type=int, default=8192)
     ap.add_argument("--cols", type=int, default=14336)
     ap.add_argument("--iters", type=int, default=5)
@@ -97,6 +102,59 @@ def main():
         vs = [torch.zeros(numel, device=dev) for _ in range(L)]
         run = lambda: MT.adamw(ps, gs, ms, vs, [1] * L, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01)
         nbytes = L * numel * 4 * 7
+    elif args.op == "clip_scale":
+        L, m, n = 4, 4096, 14336
+        ts = [torch.randn(m, n, device=dev, dtype=bf) for _ in range(L)]
+        coef = torch.full((L,), 0.999, device=dev)
+        run = lambda: MT.clip_scale(ts, list(range(L)), coef)
+        nbytes = L * m * n * 2 * 2
+    elif args.op == "cast":
+        L, m, n = 4, 4096, 14336
+        srcs = [torch.randn(m, n, device=dev) for _ in range(L)]
+        dsts = [torch.empty(m, n, device=dev, dtype=bf) for _ in range(L)]
+        run = lambda: MT.cast(srcs, dsts)
+        nbytes = L * m * n * (4 + 2)
+    elif args.op == "peer_prologue":
+        # reduce-to-owner fused with the prologue: 4 "ranks" whose gradient arenas are 4 local buffers
+        from dmuon_b200.ops import peer as P
+
+        W, L, m, n = 4, 2, 4096, 14336
+        arenas = [torch.randn(L * m * n, device=dev, dtype=bf) for _ in range(W)]
+        moms = [torch.zeros(m * n, device=dev) for _ in range(L)]
+        xs = [torch.empty(m * n, device=dev, dtype=torch.float16) for _ in range(L)]
+        sumsq = torch.zeros(L, device=dev)
+        pre = torch.ones(L, device=dev)
+        run = lambda: P.peer_prologue([a.data_ptr() for a in arenas], [i * m * n for i in range(L)], [m * n] * L, bf,
+                                      moms, xs, list(range(L)), sumsq, scale=1.0 / W, mu=0.95, nesterov=True,
+                                      xscale=pre)
+        nbytes = L * m * n * (2 * W + 4 + 4 + 2)
+    elif args.op == "peer_pull":
+        from dmuon_b200.ops import peer as P
+
+        n = 256 << 20
+        src = torch.empty(n, dtype=torch.uint8, device=dev)
+        dst = torch.empty(n, dtype=torch.uint8, device=dev)
+        run = lambda: P.peer_pull([src.data_ptr()], [dst.data_ptr()], [n], [0], None, 0, None, dev)
+        nbytes = 2 * n
+    elif args.op in ("tp_gather", "tp_apply"):
+        from dmuon_b200.ops import tp_peer as TP
+
+        T, L, m, n = 2, 2, 4096, 14336
+        if args.op == "tp_gather":
+            # column shards (the strided case) of L full matrices, read in place, prologue in the same pass
+            shards = [[torch.randn(m, n // T, device=dev, dtype=bf) for _ in range(T)] for _ in range(L)]
+            moms = [torch.zeros(m, n, device=dev) for _ in range(L)]
+            xs = [torch.empty(m, n, device=dev, dtype=torch.float16) for _ in range(L)]
+            sumsq = torch.zeros(L, device=dev)
+            jobs = [TP.ShardJob(i, shards[i][t].data_ptr(), m, n // T, t * (n // T), n) for i in range(L) for t in range(T)]
+            run = lambda: TP.gather_prologue(jobs, bf, moms, xs, list(range(L)), sumsq, mu=0.95, nesterov=True)
+            nbytes = L * m * n * (2 + 4 + 4 + 2)
+        else:
+            delta = [torch.randn(m, n, device=dev) for _ in range(L)]
+            masters = [torch.randn(m, n // T, device=dev) for _ in range(L)]
+            srcs = [d.data_ptr() + (n // T) * 4 for d in delta]           # the second rank's column slice
+            run = lambda: TP.apply_delta(srcs, [n] * L, masters, [0.998] * L)
+            nbytes = L * m * (n // T) * (4 + 4 + 4)
     else:
         L, m, n = 4, 4096, 14336
         ts = [torch.randn(m, n, device=dev, dtype=bf) for _ in range(L)]

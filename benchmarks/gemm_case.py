@@ -69,6 +69,37 @@ def _sustain(run, seconds: float, flop_per_call: float) -> dict:
     }
 
 
+def pull_linear_case(args) -> None:
+    import torch
+
+    from dmuon_b200.ops import gemm as G
+    from dmuon_b200.ops import pull_linear as PL
+
+    dev = torch.device("cuda", 0)
+    M, N, K = args.m, (args.n or args.m), args.k
+    torch.manual_seed(0)
+    x = (torch.randn(M, K, device=dev) * 0.05).bfloat16()
+    w_owner = (torch.randn(N, K, device=dev) * 0.05).bfloat16()
+    w_local = torch.zeros_like(w_owner)
+    flag = torch.full((4,), 1, dtype=torch.int32, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    times = []
+    for it in range(args.warmup + args.iters):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        PL.pull_linear(x, w_local, w_owner.data_ptr(), pub_flag=flag[1:], pub_want=1)
+        b.record()
+        torch.cuda.synchronize()
+        if it >= args.warmup:
+            times.append(a.elapsed_time(b))
+    G.check_status(dev)
+    ms = sorted(times)[len(times) // 2]
+    print(json.dumps({"case": "pull_linear (owner = second buffer on this GPU)", "tokens": M, "out": N, "in": K,
+                      "ms": round(ms, 4), "dense_tflops": round(2.0 * M * N * K / ms / 1e9, 1),
+                      "weight_mb": round(N * K * 2 / 1e6, 1)}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--m", type=int, default=4096)
@@ -90,8 +121,13 @@ def main():
                     help="also run the product back to back for this many seconds and report the sustained rate "
                          "with the SM clock and power sampled meanwhile (the regime inside a training step)")
     ap.add_argument("--cublas", action="store_true", help="also time torch.bmm on the same operands")
+    ap.add_argument("--pull-linear", action="store_true",
+                    help="the fused publish + forward GEMM (Y = X W^T while W is fetched from its owner) on ONE "
+                         "device: the owner's copy is a second buffer of this GPU; --m tokens, --n out, --k in")
     args = ap.parse_args()
     import torch
+    if args.pull_linear:
+        return pull_linear_case(args)
 
     from dmuon_b200.ops import gemm as G
 

@@ -478,6 +478,20 @@ def _setup(
     if use_peer:
         ctx.peer_runtime = peer_mod.PeerRuntime(ctx, dp_group, [st.group for st in ctx.all_states])
     model._dedicated_comm_ctx = ctx
+    # tensor-parallel gather / scatter over peer memory, one exchange per TP group (all its ranks are here)
+    ctx.tp_exchanges = {}
+    if tp_groups and want != "nccl" and want != "collective":
+        from .parallel import tp_peer as tp_peer_mod
+
+        if tp_peer_mod.tp_peer_requested():
+            all_dparams = [d for st in ctx.all_states for d in st.group.params]
+            for tpg in tp_groups.values():
+                why_not = tp_peer_mod.tp_peer_possible(device, tpg)
+                if why_not is None:
+                    mine = [d for d in all_dparams if d.tp_group is tpg]
+                    ctx.tp_exchanges[id(tpg)] = tp_peer_mod.TPPeerExchange(ctx, tpg, mine)
+                else:
+                    log.info("dedicate_params: collective tensor-parallel gather/scatter (%s)", why_not)
     ctx.ddp_on_peer_plane = ddp_on_peer
     if ddp_on_peer:
         ctx.mode = "ddp"

@@ -48,6 +48,7 @@ __global__ void __launch_bounds__(kBlock) prologue_kernel(const DmuonPrologueArg
   TX* x = reinterpret_cast<TX*>(a.x[t]);
   const long long n = a.numel[t];
   const float gs = a.gscale ? *a.gscale : 1.f;
+  const float xs = a.xscale ? a.xscale[a.slot[t]] : 1.f;
   const float mu = a.mu;
   float acc = 0.f;
   const bool vec = aligned16(g) && aligned16(m) && aligned16(x);
@@ -64,6 +65,7 @@ __global__ void __launch_bounds__(kBlock) prologue_kernel(const DmuonPrologueArg
       mv[k] = Conv<TM>::to(Conv<TM>::from(fmaf(mu, mv[k], gg)));
       uv[k] = a.nesterov ? fmaf(mu, mv[k], gg) : mv[k];
       acc = fmaf(uv[k], uv[k], acc);
+      uv[k] *= xs;
     }
     store8<TM>(m + i * kVec, mv);
     store8<TX>(x + i * kVec, uv);
@@ -74,7 +76,7 @@ __global__ void __launch_bounds__(kBlock) prologue_kernel(const DmuonPrologueArg
     const TM mn = Conv<TM>::from(fmaf(mu, Conv<TM>::to(m[i]), gg));
     m[i] = mn;
     const float u = a.nesterov ? fmaf(mu, Conv<TM>::to(mn), gg) : Conv<TM>::to(mn);
-    x[i] = Conv<TX>::from(u);
+    x[i] = Conv<TX>::from(u * xs);
     acc = fmaf(u, u, acc);
   }
   const float total = block_sum(acc);

@@ -27,6 +27,9 @@ struct DmuonPrologueArgs {
   int nesterov;
   const float* gscale;           // optional device scalar (clip coefficient)
   float* sumsq;                  // zeroed by the caller
+  // optional per-slot multiplier applied to the STORED x only (x = cast(u * xscale[slot]); sumsq stays
+  // the sum of u^2): lets a 16-bit operand be written in the same pass with a scale known beforehand
+  const float* xscale;
 };
 
 // scale[i] = 1 / (sqrt(sumsq[i]) + eps), scale2[i] = scale[i]^2

@@ -129,6 +129,7 @@ __global__ void __launch_bounds__(kBlock) peer_prologue_kernel(const DmuonPeerPr
   TX* x = reinterpret_cast<TX*>(a.x[t]);
   const long long n = a.numel[t];
   const float gs = (a.gscale ? *a.gscale : 1.f) * a.scale;
+  const float xs = a.xscale ? a.xscale[a.slot[t]] : 1.f;
   const float mu = a.mu;
   const int W = a.world;
   const TG* g[DMUON_MAX_PEERS];
@@ -174,7 +175,10 @@ __global__ void __launch_bounds__(kBlock) peer_prologue_kernel(const DmuonPeerPr
       for (int k = 0; k < kVec; ++k) uv[k] = sum[k] * gs;
     }
 #pragma unroll
-    for (int k = 0; k < kVec; ++k) acc = fmaf(uv[k], uv[k], acc);
+    for (int k = 0; k < kVec; ++k) {
+      acc = fmaf(uv[k], uv[k], acc);
+      uv[k] *= xs;
+    }
     st8<TX>(x + i * kVec, uv);
   }
   for (long long i = nvec * kVec + static_cast<long long>(blockIdx.x) * kBlock + threadIdx.x; i < n;
@@ -188,7 +192,7 @@ __global__ void __launch_bounds__(kBlock) peer_prologue_kernel(const DmuonPeerPr
       m[i] = mn;
       u = a.nesterov ? fmaf(mu, Cv<TM>::to(mn), gg) : Cv<TM>::to(mn);
     }
-    x[i] = Cv<TX>::from(u);
+    x[i] = Cv<TX>::from(u * xs);
     acc = fmaf(u, u, acc);
   }
   const float total = blk_sum(acc);

@@ -53,6 +53,7 @@ struct DmuonPeerPrologueArgs {
   long long budget_cycles;
   int* status;
   int max_blocks_per_tensor;             // 0 = default
+  const float* xscale;                   // optional per-slot multiplier of the stored x (see DmuonPrologueArgs)
 };
 
 // Pull: dst[t] (local) = src[t] (on the owner, peer-mapped) after the owner's

@@ -26,7 +26,7 @@ class _PrologueArgs(ctypes.Structure):
         ("grad", _VP), ("mom", _VP), ("x", _VP), ("numel", _LL), ("slot", _IA),
         ("n", ctypes.c_int), ("grad_dtype", ctypes.c_int), ("mom_dtype", ctypes.c_int), ("x_dtype", ctypes.c_int),
         ("mu", ctypes.c_float), ("nesterov", ctypes.c_int),
-        ("gscale", ctypes.c_void_p), ("sumsq", ctypes.c_void_p),
+        ("gscale", ctypes.c_void_p), ("sumsq", ctypes.c_void_p), ("xscale", ctypes.c_void_p),
     ]
 
 
@@ -111,9 +111,12 @@ def muon_prologue(
     mu: float,
     nesterov: bool,
     gscale: Optional[torch.Tensor] = None,
+    xscale: Optional[torch.Tensor] = None,
 ) -> None:
-    """``mom = mu*mom + g``; ``x = cast(g + mu*mom)`` (or ``mom``); accumulate
-    ``sum(x^2)`` into ``sumsq[slot]`` (``sumsq`` must be zeroed by the caller)."""
+    """``mom = mu*mom + g``; ``u = g + mu*mom`` (or ``mom``); ``x = cast(u)``;
+    accumulate ``sum(u^2)`` into ``sumsq[slot]`` (``sumsq`` must be zeroed by the
+    caller).  With ``xscale`` (fp32, one entry per slot) the stored operand is
+    ``cast(u * xscale[slot])`` while the sum of squares stays that of ``u``."""
     n = len(grads)
     assert n == len(moms) == len(xs) == len(slots)
     if n == 0:
@@ -135,6 +138,7 @@ def muon_prologue(
         a.mu, a.nesterov = float(mu), int(bool(nesterov))
         a.gscale = gscale.data_ptr() if gscale is not None else None
         a.sumsq = sumsq.data_ptr()
+        a.xscale = xscale.data_ptr() if xscale is not None else None
         _check(_lib().dmuon_muon_prologue(ctypes.byref(a), _stream(dev)), "dmuon_muon_prologue")
 
 

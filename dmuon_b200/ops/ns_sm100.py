@@ -73,11 +73,20 @@ class _Workspace:
         self.scale = torch.empty(L, device=device, dtype=torch.float32)
         self.scale2 = torch.empty(L, device=device, dtype=torch.float32)
         self.Xf32: Optional[torch.Tensor] = None
+        # single-pass fp16 operand: the per-matrix correction factors of the current call
+        self.fix = torch.empty(L, device=device, dtype=torch.float32)
+        self.fix2 = torch.empty(L, device=device, dtype=torch.float32)
 
     def nbytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in vars(self).values() if isinstance(t, torch.Tensor))
 
 
+#: fp16 Gram operands written by the prologue itself from the second step on (no fp32 staging pass);
+#: ``DMUON_NS_SINGLE_PASS=0`` keeps the two-pass form (norm first, then cast)
+SINGLE_PASS_FP16 = __import__("os").environ.get("DMUON_NS_SINGLE_PASS", "1").strip().lower() not in ("0", "false", "no", "off")
+
+#: per batch of matrices (keyed by their momentum buffers): K / ||u|| of their previous step
+_prescales: dict[tuple, torch.Tensor] = {}
 _workspaces: dict[tuple, _Workspace] = {}
 _ptr_tables: dict[tuple, torch.Tensor] = {}
 MAX_WORKSPACE_BYTES = 6 << 30
@@ -98,6 +107,7 @@ def workspace(L: int, m0: int, n0: int, dtype: torch.dtype, device) -> _Workspac
 def release_workspaces() -> None:
     _workspaces.clear()
     _ptr_tables.clear()
+    _prescales.clear()
 
 
 def max_batch(m0: int, n0: int, itemsize: int = 2) -> int:
@@ -401,28 +411,47 @@ def muon_update_batched(
     m0, n0 = int(moms[0].shape[0]), int(moms[0].numel() // moms[0].shape[0])
     dev = moms[0].device
 
-    def prologue(xs_out):
-        if peer is not None:
+    def prologue(xs_out, xscale=None):
+        if peer is not None and hasattr(peer, "launch_prologue"):
+            # tensor-parallel gather fused into the prologue: every shard is read where it lies
+            peer.launch_prologue(moms, xs_out, slots, ws.sumsq, mu=mu, nesterov=nesterov, gscale=gscale,
+                                 xscale=xscale)
+        elif peer is not None:
             # reduce-to-owner fused into the prologue: gradients are read from
             # every rank's arena through its peer mapping
             from . import peer as P
 
             P.peer_prologue(peer.peer_bases, peer.offsets, peer.numels, peer.grad_dtype, moms, xs_out, slots,
                             ws.sumsq, scale=peer.scale, mu=mu, nesterov=nesterov, gscale=gscale,
-                            ready_flags=peer.ready_flags, ready_want=peer.ready_want, status=peer.status)
+                            ready_flags=peer.ready_flags, ready_want=peer.ready_want, status=peer.status,
+                            xscale=xscale)
         else:
-            MT.muon_prologue(grads, moms, xs_out, slots, ws.sumsq, mu, nesterov, gscale)
+            MT.muon_prologue(grads, moms, xs_out, slots, ws.sumsq, mu, nesterov, gscale, xscale=xscale)
 
     cd = _resolve_dtype(compute_dtype, formulation)
     ws = workspace(L, m0, n0, cd, dev)
     left = m0 <= n0
     ws.sumsq.zero_()
     slots = list(range(L))
+    owner_key = tuple(m.data_ptr() for m in moms)     # which matrices: their momentum buffers live as long as they do
     if cd == torch.bfloat16 and formulation == "gram":
         # one pass: the raw bf16 operand carries its scale as a per-matrix vector
         prologue([ws.X[i].reshape(-1) for i in range(L)])
         MT.norm_scales(ws.sumsq, ws.scale, ws.scale2, eps)
         xscale = _XScale(vec=ws.scale, vec2=ws.scale2)
+    elif cd == torch.float16 and formulation == "gram" and SINGLE_PASS_FP16 and owner_key in _prescales:
+        # one pass: the fp16 operand is stored with LAST step's K / ||u|| of the same matrices (momentum
+        # makes the norm drift slowly, and fp16 has three orders of magnitude of room on either side of
+        # the entries' size), and the products carry the exact correction ||u||_prev / ||u||_now per
+        # matrix, so the result is scaled by this step's true norm
+        K = fp16_prescale(m0, n0)
+        pre = _prescales[owner_key]
+        prologue([ws.X[i].reshape(-1) for i in range(L)], xscale=pre)
+        MT.norm_scales(ws.sumsq, ws.scale, ws.scale2, eps)
+        torch.div(ws.scale, pre, out=ws.fix)                  # (1/||u||) / (K/||u||_prev)
+        torch.mul(ws.fix, ws.fix, out=ws.fix2)
+        torch.mul(ws.scale, K, out=pre)                       # what the next step stores with
+        xscale = _XScale(vec=ws.fix, vec2=ws.fix2)
     else:
         # two passes: fp32 staging, then normalise (and prescale fp16) while casting
         if ws.Xf32 is None:
@@ -435,6 +464,11 @@ def muon_update_batched(
             ws.scale.mul_(K)
         MT.cast(stage, [ws.X[i] for i in range(L)], scale=ws.scale, slots=slots)
         xscale = _XScale(h=1.0 / K)
+        if cd == torch.float16 and formulation == "gram" and SINGLE_PASS_FP16:
+            # from the next step on these matrices take the single-pass path (ws.scale holds K / ||u||)
+            if len(_prescales) > 4096:
+                _prescales.clear()
+            _prescales[owner_key] = ws.scale.clone()
 
     step_alpha = -float(lr) * float(update_scale)
     if formulation == "direct":

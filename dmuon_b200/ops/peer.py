@@ -36,7 +36,7 @@ class _PeerPrologueArgs(ctypes.Structure):
         ("n", ctypes.c_int), ("grad_dtype", ctypes.c_int), ("mom_dtype", ctypes.c_int), ("x_dtype", ctypes.c_int),
         ("mu", ctypes.c_float), ("nesterov", ctypes.c_int), ("gscale", ctypes.c_void_p), ("sumsq", ctypes.c_void_p),
         ("ready_flags", ctypes.c_void_p), ("ready_want", ctypes.c_int), ("budget_cycles", ctypes.c_longlong),
-        ("status", ctypes.c_void_p), ("max_blocks_per_tensor", ctypes.c_int),
+        ("status", ctypes.c_void_p), ("max_blocks_per_tensor", ctypes.c_int), ("xscale", ctypes.c_void_p),
     ]
 
 
@@ -169,6 +169,7 @@ def peer_prologue(
     status: Optional[torch.Tensor] = None,
     budget_cycles: Optional[int] = None,
     max_blocks_per_tensor: int = 0,
+    xscale: Optional[torch.Tensor] = None,
 ) -> None:
     """Sum the gradient of every listed tensor over all ranks' arenas (peer
     loads, rank order), scale, then momentum / Nesterov / cast / sum of squares
@@ -202,6 +203,7 @@ def peer_prologue(
         a.budget_cycles = int(budget_cycles if budget_cycles is not None else wait_budget_cycles())
         a.status = status.data_ptr() if status is not None else None
         a.max_blocks_per_tensor = int(max_blocks_per_tensor)
+        a.xscale = xscale.data_ptr() if xscale is not None else None
         _check(_lib().dmuon_peer_prologue(ctypes.byref(a), _stream(dev)), "dmuon_peer_prologue")
 
 

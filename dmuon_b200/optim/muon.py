@@ -547,6 +547,8 @@ class Muon(torch.optim.Optimizer):
             if rt is not None:
                 rt.after_optimizer_consumed()
                 rt.publish_owned()
+            for ex in (getattr(self.comm_ctx, "tp_exchanges", None) or {}).values():
+                ex.after_step()
             if len(blocks) == 1:
                 for g in groups:
                     g.post_step_publish_async()
@@ -572,6 +574,10 @@ class Muon(torch.optim.Optimizer):
             rt.announce_grads()
             if materialize:
                 rt.materialize([dp for dp in self._all_dedicated if dp.is_owner])
+        if materialize:
+            for dp in self._all_dedicated:
+                if hasattr(dp._tp_full_grad, "materialize"):
+                    dp._tp_full_grad.materialize()
 
     # ------------------------------------------------------------------ Muon
     def _momentum_of(self, dp, shape, device) -> torch.Tensor:
@@ -621,6 +627,8 @@ class Muon(torch.optim.Optimizer):
             rt = self.comm_ctx.peer_runtime
             rt.materialize([dp for dp, g in work if g is None])
             work = [(dp, dp._reduced_grad) for dp, _ in work]
+        if not use_kernels:
+            work = [(dp, g.materialize() if hasattr(g, "materialize") else g) for dp, g in work]
         if use_kernels:
             self._step_muon_kernels(work, lr, mu, wd, gscale)
         else:
@@ -724,7 +732,10 @@ class Muon(torch.optim.Optimizer):
             if dp.is_tp_owner:
                 if dp._tp_full_grad is None:
                     raise RuntimeError(f"{dp.param_name}: the TP gather did not deliver the full gradient to its TP owner")
-                fg = dp._tp_full_grad.reshape(rows, cols).to(dp._optim_dtype)
+                full = dp._tp_full_grad
+                if hasattr(full, "materialize"):
+                    full = full.materialize()       # shards still in the TP peers' buffers
+                fg = full.reshape(rows, cols).to(dp._optim_dtype)
                 if gscale is not None:
                     fg = fg * gscale.to(fg.dtype)
                 fbuf = self._momentum_of(dp, (rows, cols), fg.device)
@@ -790,6 +801,12 @@ class Muon(torch.optim.Optimizer):
                     # reduce-to-owner happens inside the prologue kernel
                     grads = None
                     peer = rt.source_for([dp for dp, _ in chunk])
+                elif gdt == "tp_peer":
+                    # tensor-parallel gather happens inside the prologue kernel
+                    from ..parallel.tp_peer import TPGatherSource
+
+                    grads = None
+                    peer = TPGatherSource([g for _, g in chunk])
                 else:
                     peer = None
                     grads = [g.reshape(rows, cols) if g.is_contiguous() else g.reshape(rows, cols).contiguous() for _, g in chunk]
@@ -799,7 +816,16 @@ class Muon(torch.optim.Optimizer):
                     compute_dtype=self.ns.compute_dtype, gscale=gscale, peer=peer,
                 )
                 if is_tp:
-                    deltas = [torch.empty(dp.full_shape, dtype=torch.float32, device=self.device) for dp, _ in chunk]
+                    exchanges = getattr(self.comm_ctx, "tp_exchanges", None) or {}
+                    deltas = []
+                    for dp, _ in chunk:
+                        ex = exchanges.get(id(dp.tp_group))
+                        if ex is not None:
+                            # written where the TP peers will pull their slices from
+                            ex.before_delta_writes()
+                            deltas.append(ex.delta_view(dp))
+                        else:
+                            deltas.append(torch.empty(dp.full_shape, dtype=torch.float32, device=self.device))
                     ns_sm100.muon_update_batched(grads, moms, None, deltas=deltas, **common)
                     for (dp, _), d in zip(chunk, deltas):
                         dp._tp_full_delta = d
@@ -807,7 +833,8 @@ class Muon(torch.optim.Optimizer):
                     masters = [dp._owned_data for dp, _ in chunk]
                     publish = [getattr(dp, "_publish_view", None) for dp, _ in chunk]
                     multicast = None
-                    if rt is not None and rt.copy_mode == "nvls" and all(p is not None for p in publish):
+                    nvls = rt is not None and rt.copy_mode == "nvls" and all(p is not None for p in publish)
+                    if nvls and rt.nvls_publish == "epilogue":
                         if cols % 8 == 0:
                             # the last product stores the bf16 weights through the NVSwitch multicast
                             # mapping of the publish arena: they land on every rank while it runs
@@ -817,6 +844,10 @@ class Muon(torch.optim.Optimizer):
                             publish = [None] * len(chunk)       # published (cast + multicast) after the step
                     wrote = ns_sm100.muon_update_batched(grads, moms, masters, publish=publish,
                                                          publish_multicast=multicast, **common)
+                    if nvls and wrote and multicast is None:
+                        # the last product wrote the local slots: replicate them to all ranks on the
+                        # publish lane while the next batch is orthogonalised
+                        rt.multicast_publish_async([dp for dp, _ in chunk])
                     for dp, _ in chunk:
                         dp._publish_fresh = bool(wrote)
 

@@ -443,6 +443,18 @@ class DedicatedParamGroup:
         lane = lane or self.comm_ctx.reduce_lane
         lane.follow_current()
         keep = []
+        exchanges = getattr(self.comm_ctx, "tp_exchanges", None) or {}
+        peer_todo = [p for p in todo if id(p.tp_group) in exchanges]
+        if peer_todo:
+            # peer-memory gather: shards go into the TP group's symmetric buffer, the owner's prologue
+            # reads them in place (parallel/tp_peer.py)
+            todo = [p for p in todo if id(p.tp_group) not in exchanges]
+            with lane.use(), torch.no_grad():
+                by_group: dict[int, list] = defaultdict(list)
+                for p in peer_todo:
+                    by_group[id(p.tp_group)].append(p)
+                for gid, plist in by_group.items():
+                    exchanges[gid].publish_shards(plist)
         with lane.use(), torch.no_grad():
             with record_function(f"dmuon.tp_gather.{self.name}"):
                 for p in todo:
@@ -485,6 +497,17 @@ class DedicatedParamGroup:
         lane = lane or self.comm_ctx.replicate_broadcast_lane
         lane.follow_current()
         lane.follow(self.comm_ctx.reduce_lane)      # gather and scatter share the TP communicator
+        exchanges = getattr(self.comm_ctx, "tp_exchanges", None) or {}
+        peer_todo = [p for p in todo if id(p.tp_group) in exchanges]
+        if peer_todo:
+            # peer-memory scatter: every rank pulls its slice of the owner's update and applies it
+            todo = [p for p in todo if id(p.tp_group) not in exchanges]
+            with lane.use(), torch.no_grad():
+                by_group: dict[int, list] = defaultdict(list)
+                for p in peer_todo:
+                    by_group[id(p.tp_group)].append(p)
+                for gid, plist in by_group.items():
+                    exchanges[gid].scatter_apply(plist)
         with lane.use(), torch.no_grad():
             with record_function(f"dmuon.tp_scatter.{self.name}"):
                 for p in todo:

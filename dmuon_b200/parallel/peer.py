@@ -58,7 +58,26 @@ ALIGN = 64          # elements; keeps every slot 128-byte aligned for bf16
 REDUCE_BLOCKS_PER_TENSOR = 24
 #: CTAs of the per-layer in-switch gradient reduce that runs beside the backward GEMMs: each 16-byte
 #: reduce-load returns data already summed over all ranks, so a few CTAs keep up with a layer
+#: (16 CTAs moved 105 GB/s on two B200s: 2 ms for a layer's 218 MB, against 8 ms of backward per layer)
 NVLS_REDUCE_BLOCKS = 16
+#: CTAs of the multicast publish that runs beside the Newton-Schulz products of the next shape batch
+NVLS_PUBLISH_BLOCKS = 16
+
+
+def nvls_publish_mode() -> str:
+    """``DMUON_NVLS_PUBLISH``: how the owner's new bf16 weights reach the other
+    ranks on the NVSwitch plane.  ``lane`` (default): the update kernel writes
+    the local arena slot and a copy kernel on the publish lane stores the slot
+    through the multicast mapping with fully coalesced 16-byte stores, while the
+    next batch of Newton-Schulz products runs.  ``epilogue``: the last product's
+    epilogue issues the ``multimem.st`` itself, tile by tile (one kernel does the
+    GEMM and the broadcast); its stores are 16 bytes per row and lane, which the
+    links carry at about a quarter of the coalesced rate (measured on two B200s:
+    +58 ms per step for 7 GB), so it is the option, not the default."""
+    mode = os.environ.get("DMUON_NVLS_PUBLISH", "lane").strip().lower()
+    if mode not in ("lane", "epilogue"):
+        raise ValueError("DMUON_NVLS_PUBLISH must be 'lane' or 'epilogue'")
+    return mode
 #: value of the guard words around the arenas in canary mode (exact in bf16, fp16 and fp32)
 CANARY_VALUE = -1.5
 
@@ -338,6 +357,8 @@ class PeerRuntime:
         self.reduced_base = 0
         self._consumed_signalled_epoch = 0
         self._ready_waited_epoch = 0
+        self.nvls_publish = nvls_publish_mode()
+        self._publish_ticket = None
         if self.copy_mode == "nvls":
             span = max(self.own_hi - self.own_lo, ALIGN)
             self.reduced = torch.zeros(span, dtype=self.grad_dtype, device=self.device)
@@ -497,6 +518,33 @@ class PeerRuntime:
         with record_function(f"dmuon.peer.publish_owned.{self.copy_mode}.epoch{self.pub_epoch + 1}.stale{len(stale)}"):
             self._publish_owned(stale, MT)
 
+    def _multicast_slots(self, plist: list[DedicatedParam], blocks: int = 0) -> None:
+        """Store the local publish slots of ``plist`` to every rank's arena
+        (current stream); adjacent slots travel as one span."""
+        from ..ops import peer as P
+
+        esz = self.pub.element_size()
+        spans: list[list[int]] = []
+        for p in sorted(plist, key=lambda q: q._arena_offset):
+            lo = p._arena_offset * esz
+            hi = lo + (p.numel + ALIGN - 1) // ALIGN * ALIGN * esz
+            if spans and spans[-1][1] == lo:
+                spans[-1][1] = hi
+            else:
+                spans.append([lo, hi])
+        P.multicast_broadcast([self.pub.data_ptr() + lo for lo, _ in spans], [self.pub_mc + lo for lo, _ in spans],
+                              [hi - lo for lo, hi in spans], self.device, blocks_per_tensor=blocks)
+
+    def multicast_publish_async(self, plist: list[DedicatedParam]) -> None:
+        """NVSwitch plane, ``lane`` mode: the update kernel has just written the
+        local slots of ``plist``; replicate them to all ranks on the publish
+        lane while the optimizer goes on with the next batch."""
+        lane = self.ctx.broadcast_lane
+        lane.follow_current()
+        with lane.use(), record_function(f"dmuon.peer.multicast_publish.params{len(plist)}"):
+            self._multicast_slots(plist, NVLS_PUBLISH_BLOCKS)
+        self._publish_ticket = lane.mark()
+
     def _publish_owned(self, stale, MT) -> None:
         if stale:
             srcs = [p._owned_data.reshape(-1) for p in stale]
@@ -507,16 +555,14 @@ class PeerRuntime:
                 else:
                     torch._foreach_copy_(dsts, srcs)
                 if self.copy_mode == "nvls":
-                    # slots the update kernel did not multicast itself (AdamW-routed tensors, the first
+                    # slots that were not multicast during the step (AdamW-routed tensors, the first
                     # publish, a checkpoint load): replicate the local copy to every rank's arena
-                    from ..ops import peer as P
-
-                    esz = self.pub.element_size()
-                    spans = [(p._arena_offset * esz, (p.numel + ALIGN - 1) // ALIGN * ALIGN * esz) for p in stale]
-                    P.multicast_broadcast(
-                        [self.pub.data_ptr() + off for off, _ in spans], [self.pub_mc + off for off, _ in spans],
-                        [nb for _, nb in spans], self.device,
-                    )
+                    self._multicast_slots(stale)
+        if self._publish_ticket is not None:
+            # multicast stores queued on the publish lane during the step must be complete before
+            # the new epoch is announced
+            self._publish_ticket.wait_on_current()
+            self._publish_ticket = None
         for g in self.groups:
             for p in g.bcast_params:
                 p._publish_fresh = False

@@ -328,6 +328,46 @@ def test_muon_update_batched_matches_reference_math(cdt):
         assert (pubs[i].float() - masters[i]).abs().max().item() < 1e-2 * masters[i].abs().max().item()
 
 
+def test_muon_update_single_pass_operand_on_later_steps():
+    """From the second step on the fp16 Gram operand is written by the prologue
+    itself, scaled with the previous step's norm, and the products carry the
+    exact correction.  Three steps whose gradient norms differ by factors of 5
+    and 1/20 must still match fp32 math step by step."""
+    from dmuon_b200.ops import gemm as G
+    from dmuon_b200.ops import ns_sm100
+    from dmuon_b200.optim import newton_schulz as NS
+
+    dev = _dev()
+    torch.manual_seed(8)
+    L, m, n = 3, 512, 1024
+    moms = [torch.zeros(m, n, device=dev) for _ in range(L)]
+    masters = [torch.randn(m, n, device=dev) * 0.02 for _ in range(L)]
+    ref_m = [x.clone() for x in moms]
+    ref_w = [x.clone() for x in masters]
+    coefs, restarts = list(NS.POLAR_EXPRESS_COEFFICIENTS), [2]
+    lr, wd, mu = 0.02, 0.1, 0.9
+    scale = 0.2 * math.sqrt(max(m, n))
+    ns_sm100.release_workspaces()
+    for step, gmag in enumerate([1e-3, 5e-3, 2.5e-4]):
+        grads = [(torch.randn(m, n, device=dev) * gmag).bfloat16() for _ in range(L)]
+        ns_sm100.muon_update_batched(grads, moms, masters, mu=mu, nesterov=True, coefs=coefs, restarts=restarts,
+                                     formulation="gram", lr=lr, weight_decay=wd, update_scale=scale)
+        torch.cuda.synchronize()
+        G.check_status(dev)
+        assert (tuple(x.data_ptr() for x in moms) in ns_sm100._prescales) == ns_sm100.SINGLE_PASS_FP16
+        for i in range(L):
+            g = grads[i].float()
+            ref_m[i] = mu * ref_m[i] + g
+            u = g + mu * ref_m[i]
+            o = NS.gram_newton_schulz(u, coefficients=coefs, restart_iterations=restarts, deterministic=True,
+                                      compute_dtype=torch.float32)
+            ref_w[i] = ref_w[i] * (1 - lr * wd) - lr * scale * o
+            assert torch.allclose(moms[i], ref_m[i], atol=1e-6), step
+            err = (masters[i] - ref_w[i]).abs().max().item()
+            assert err < 0.1 * lr * scale * (step + 1), (step, err)
+            ref_w[i] = masters[i].clone()        # compare each step on its own, not the accumulated drift
+
+
 def test_newton_schulz_graph_replay_matches_eager(monkeypatch):
     """Stand-alone NS through the CUDA-graph cache: eager on the first call,
     captured on the second, replayed afterwards, same numbers as eager."""
@@ -391,3 +431,49 @@ def test_gram_factors_on_kernels_reproduce_newton_schulz(shape):
     G.check_status(dev)
     assert got.dtype == torch.float32 and got.shape == U.shape
     assert (got - ref).abs().max().item() < 2e-2 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("shard_dim", [0, 1])
+@pytest.mark.parametrize("cols", [256, 250])          # 250: narrow shards that are not a multiple of 8 wide
+def test_tp_gather_prologue_and_apply_delta(shard_dim, cols):
+    """The tensor-parallel kernels on one device (the shards of the "other
+    ranks" are just other allocations): shards written into their place of the
+    full matrix with momentum / Nesterov / cast / norm in the same pass, and the
+    slice of a full update applied to a master shard."""
+    from dmuon_b200.ops import tp_peer as TP
+
+    dev = _dev()
+    torch.manual_seed(13)
+    T, rows, mu = 2, 192, 0.9
+    full_g = (torch.randn(rows, cols, device=dev) * 1e-2).bfloat16()
+    shards = [c.contiguous() for c in full_g.chunk(T, dim=shard_dim)]
+    mom = torch.randn(rows, cols, device=dev) * 1e-2
+    mom0 = mom.clone()
+    x = torch.full((rows, cols), float("nan"), device=dev, dtype=torch.float16)
+    sumsq = torch.zeros(2, device=dev)
+    xscale = torch.tensor([1.0, 4.0], device=dev)
+    jobs = []
+    for t, s in enumerate(shards):
+        r_off = t * s.shape[0] if shard_dim == 0 else 0
+        c_off = t * s.shape[1] if shard_dim == 1 else 0
+        jobs.append(TP.ShardJob(0, s.data_ptr(), s.shape[0], s.shape[1], r_off * cols + c_off, cols))
+    TP.gather_prologue(jobs, torch.bfloat16, [mom], [x], [1], sumsq, mu=mu, nesterov=True, xscale=xscale)
+    torch.cuda.synchronize()
+    buf = mu * mom0 + full_g.float()
+    u = full_g.float() + mu * buf
+    assert torch.allclose(mom, buf, atol=1e-7)
+    assert (x.float() - 4.0 * u).abs().max().item() < 2e-3 * (4.0 * u).abs().max().item()
+    assert abs(float(sumsq[1]) - float((u * u).sum())) < 1e-3 * float((u * u).sum()) and float(sumsq[0]) == 0.0
+    # scatter side: every "rank" applies its slice of the owner's full fp32 update to its master shard
+    delta = torch.randn(rows, cols, device=dev) * 1e-3
+    masters = [torch.randn_like(s, dtype=torch.float32) for s in shards]
+    before = [m.clone() for m in masters]
+    srcs = []
+    for t, s in enumerate(shards):
+        r_off = t * s.shape[0] if shard_dim == 0 else 0
+        c_off = t * s.shape[1] if shard_dim == 1 else 0
+        srcs.append(delta.data_ptr() + (r_off * cols + c_off) * 4)
+    TP.apply_delta(srcs, [cols] * T, masters, [0.998] * T)
+    torch.cuda.synchronize()
+    for m, b, d in zip(masters, before, delta.chunk(T, dim=shard_dim)):
+        assert torch.allclose(m, b * 0.998 + d, atol=1e-6)

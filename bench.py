@@ -53,6 +53,19 @@ def pi0_host_batch(dims, mb, gen):
 PUBLISHED_OVERHEAD_VS_ADAMW = 1.08
 
 
+def mfu(args, dims, tokens_per_step, step_ms, world):
+    if args.model == "pi0":
+        return None
+    d, L, ffn, v = dims["d_model"], dims["n_layers"], dims["ffn_hidden"], dims["vocab_size"]
+    kv = dims["n_kv_heads"] * dims["head_dim"]
+    q = dims["n_heads"] * dims["head_dim"]
+    per_layer = d * q + 2 * d * kv + q * d + 3 * d * ffn
+    params = L * per_layer + v * d                      # lm_head; the embedding lookup costs no FLOPs
+    attn = 6 * L * q * dims["seq"]                      # causal: half of 12 * L * d_attn * seq per token
+    flops = tokens_per_step * (6 * params + attn)
+    return round(flops / (step_ms / 1e3) / (world * 2250e12), 4)
+
+
 def adamw_step_ms(args, world):
     """FSDP2 + fused AdamW step time of the same model, placement and GPU count,
     measured on this pool with ``--optimizer adamw`` and recorded in
@@ -212,14 +225,20 @@ def _plane_name(ctx) -> str:
     rt = getattr(ctx, "peer_runtime", None)
     if rt is None:
         return "nccl"
-    if rt.copy_mode == "nvls":
+    reduce = {
+        "nvls": "gradients summed in the switch per layer during backward (multimem.ld_reduce), one reduced copy read by the Muon prologue kernel",
+        "ce": "copy-engine gradient gather, sum fused into the Muon prologue kernel",
+        "sm": "gradients read through peer mappings by the Muon prologue kernel",
+    }[rt.reduce_via]
+    if rt.publish_via == "nvls":
         how = ("by the update GEMM's epilogue" if rt.nvls_publish == "epilogue"
                else "by a copy kernel on the publish lane while the next Newton-Schulz batch runs")
-        return (f"NVSwitch multicast: weights stored to all ranks {how} (multimem.st), "
-                "gradients summed in the switch per layer during backward (multimem.ld_reduce)")
-    if rt.copy_mode == "ce":
-        return "peer memory: copy-engine pulls and gradient gather, sum fused into the Muon prologue kernel"
-    return "peer-memory kernels (loads through peer mappings)"
+        publish = f"weights stored to all ranks {how} (multimem.st)"
+    elif rt.publish_via == "ce":
+        publish = "weights pulled by the readers' copy engines"
+    else:
+        publish = "weights pulled by a kernel through peer mappings"
+    return f"peer memory [{rt.copy_mode}]: {publish}; {reduce}"
 
 
 def _pred(name, p):
@@ -581,6 +600,9 @@ def run(args):
             "data": "synthetic uniform token ids, random-init weights N(0, 0.02)",
             "impl": args.impl,
             "tokens_per_s": round(tokens / (step_ms / 1e3), 1),
+            # model FLOP utilisation: 6 FLOPs per parameter and token plus causal attention, against the
+            # nominal dense bf16 peak of a B200 (2250 TFLOP/s per GPU); null for the vision-language model
+            "mfu": mfu(args, dims, tokens, step_ms, world),
             "optimizer_step_ms": round(opt_ms, 3),
             "fwd_bwd_ms": round(step_ms - opt_ms, 3),
             "loss": last_loss,

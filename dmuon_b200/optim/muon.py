@@ -772,6 +772,7 @@ class Muon(torch.optim.Optimizer):
                 w.mul_(1.0 - lr * wd)
             w.add_(upd.reshape(w.shape).to(w.dtype), alpha=-lr * muon_update_scale((rows, cols)))
             dp._tp_full_grad = dp._tp_full_delta = dp._reduced_grad = None
+            dp._tp_gathered = False
             dp._tp_wd_factor = 1.0
 
     def _step_muon_kernels(self, work, lr, mu, wd, gscale) -> None:
@@ -833,7 +834,7 @@ class Muon(torch.optim.Optimizer):
                     masters = [dp._owned_data for dp, _ in chunk]
                     publish = [getattr(dp, "_publish_view", None) for dp, _ in chunk]
                     multicast = None
-                    nvls = rt is not None and rt.copy_mode == "nvls" and all(p is not None for p in publish)
+                    nvls = rt is not None and rt.publish_via == "nvls" and all(p is not None for p in publish)
                     if nvls and rt.nvls_publish == "epilogue":
                         if cols % 8 == 0:
                             # the last product stores the bf16 weights through the NVSwitch multicast
@@ -948,6 +949,7 @@ class Muon(torch.optim.Optimizer):
             dp._sharded_adamw_grad = None
             dp._accumulated_grad = None
             dp._tp_full_grad = None
+            dp._tp_gathered = False
             dp._peer_grad_pending = False
             if dp.mode == "ddp":
                 dp.clear_local_grad()

@@ -418,8 +418,10 @@ class DedicatedParamGroup:
                     v = pack.view_of(i)
                     if p._reduced_grad is None:
                         p._reduced_grad = v
+                        p._tp_gathered = False
                     else:
                         p._reduced_grad = p._reduced_grad + v.to(p._reduced_grad.dtype)
+                        p._tp_gathered = False
             for p, out in self._pending_flat:
                 if p._sharded_adamw_grad is None:
                     p._sharded_adamw_grad = out
@@ -437,9 +439,18 @@ class DedicatedParamGroup:
     def tp_gather_grads(self, lane: Optional[Lane] = None) -> None:
         """Collect the reduced shards of every TP-sharded parameter on its TP
         owner.  Every TP peer of a DP owner takes part, in parameter order."""
-        todo = [p for p in self.tp_params if p.is_owner and p._dmuon_route == "muon" and p._reduced_grad is not None]
+        # a parameter is gathered ONCE per reduced gradient: a second call in the same step (gradient clipping
+        # prepares the gradients, then the optimizer step prepares them again) must not fetch the shards anew,
+        # that would replace the already clipped full gradient with the unclipped one
+        todo = [
+            p for p in self.tp_params
+            if p.is_owner and p._dmuon_route == "muon" and p._reduced_grad is not None
+            and not getattr(p, "_tp_gathered", False)
+        ]
         if not todo:
             return
+        for p in todo:
+            p._tp_gathered = True
         lane = lane or self.comm_ctx.reduce_lane
         lane.follow_current()
         keep = []
@@ -533,6 +544,7 @@ class DedicatedParamGroup:
                     p._tp_full_delta = None
                     p._tp_full_grad = None
                     p._reduced_grad = None
+                    p._tp_gathered = False
         return lane.mark()
 
     # ------------------------------------------------------------------ replicate-axis publish

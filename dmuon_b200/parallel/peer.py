@@ -13,15 +13,16 @@ gradient arena  each rank's local gradients.  Nothing is sent after backward:
                 1/N and applies momentum / Nesterov / cast / Frobenius norm in
                 the same pass.
 
-Bulk data crosses NVLink in one of three ways (``DMUON_PEER_COPY``).  "nvls"
-(chosen by "auto", the default, when the symmetric buffers have an NVSwitch
-multicast mapping): the owner's last Newton-Schulz GEMM stores the new bf16
-weights with ``multimem.st``, so they land in every rank's arena while the
-product is still running and readers copy nothing; gradients are summed inside
-the switch -- per layer, during backward, a small kernel on the reduce lane
-reads the owner's span through the multicast mapping with
-``multimem.ld_reduce`` and keeps ONE reduced copy, which the Muon prologue then
-reads locally.  "ce": copy-engine transfers.  Readers pull publish spans with asynchronous
+Bulk data crosses NVLink in one of these ways (``DMUON_PEER_COPY``).  "nvls"
+(needs an NVSwitch multicast mapping of the symmetric buffers): the owner's new
+bf16 weights are stored with ``multimem.st`` -- by a copy kernel beside the next
+Newton-Schulz batch, or by the last Newton-Schulz GEMM's own epilogue -- so they
+land in every rank's arena and readers copy nothing; gradients are summed inside
+the switch: per layer, during backward, a small kernel on the reduce lane reads
+the owner's span through the multicast mapping with ``multimem.ld_reduce`` and
+keeps ONE reduced copy, which the Muon prologue then reads locally.  "hybrid"
+(what "auto" picks where the mapping exists): that in-switch reduce, with the
+publish left to the readers' copy engines.  "ce": copy-engine transfers.  Readers pull publish spans with asynchronous
 copies, owners gather the peers' gradient slices of each layer into local
 staging buffers while backward is still running, and the fixed-order fp32 sum
 runs locally inside the Muon prologue; no SM is taken from the forward and
@@ -62,6 +63,13 @@ REDUCE_BLOCKS_PER_TENSOR = 24
 NVLS_REDUCE_BLOCKS = 16
 #: CTAs of the multicast publish that runs beside the Newton-Schulz products of the next shape batch
 NVLS_PUBLISH_BLOCKS = 16
+
+
+#: what ``DMUON_PEER_COPY=auto`` means.  "hybrid": gradients are summed inside the NVSwitch
+#: (``multimem.ld_reduce``: one reduced copy on the owner instead of N - 1 staged slices, the prologue reads
+#: 1/N of the bytes), weights are pulled by the readers' copy engines during forward (which costs the
+#: optimizer step nothing).  Falls back to "ce" where the arenas have no multicast mapping.
+AUTO_COPY_MODE = "hybrid"
 
 
 def nvls_publish_mode() -> str:
@@ -105,7 +113,7 @@ def peer_backend_possible(device: torch.device, dp_group, replicate_group, dpara
     if len({p._param_dtype for p in dparams}) != 1 or len({p._grad_dtype or p._param_dtype for p in dparams}) != 1:
         return "mixed publish or gradient dtypes"
     try:
-        import torch.distributed._symmetric_memory  # noqa: F401
+        import torch.distributed._symmetric_memory as _symm  # noqa: F401
     except Exception as exc:  # pragma: no cover
         return f"symmetric memory unavailable: {exc}"
     return None
@@ -137,7 +145,7 @@ def peer_backend_possible_from_policies(device, dp_group, replicate_group, param
     if len(pub) != 1 or len(grad) != 1:
         return "mixed publish or gradient dtypes"
     try:
-        import torch.distributed._symmetric_memory  # noqa: F401
+        import torch.distributed._symmetric_memory as _symm  # noqa: F401
     except Exception as exc:  # pragma: no cover
         return f"symmetric memory unavailable: {exc}"
     return None
@@ -147,10 +155,10 @@ class PeerSource:
     """What the fused prologue needs to read one batch of gradients."""
 
     def __init__(self, rt: "PeerRuntime", dparams: list[DedicatedParam]):
-        if rt.copy_mode == "nvls":
+        if rt.reduce_via == "nvls":
             # the in-switch sum of all ranks' slices already sits in ONE local buffer
             self.peer_bases = [rt.reduced_base]
-        elif rt.copy_mode == "ce":
+        elif rt.reduce_via == "ce":
             # the peers' slices were gathered into local staging buffers during backward
             self.peer_bases = rt.stage_bases
         else:
@@ -323,25 +331,28 @@ class PeerRuntime:
         self.pub_mc = int(getattr(self.pub_hdl, "multicast_ptr", 0) or 0)
         self.grad_mc = int(getattr(self.grad_hdl, "multicast_ptr", 0) or 0)
         self.copy_mode = os.environ.get("DMUON_PEER_COPY", "auto").strip().lower()
-        if self.copy_mode not in ("auto", "nvls", "ce", "sm"):
-            raise ValueError("DMUON_PEER_COPY must be 'auto', 'nvls', 'ce' or 'sm'")
+        if self.copy_mode not in ("auto", "nvls", "hybrid", "ce", "sm"):
+            raise ValueError("DMUON_PEER_COPY must be 'auto', 'nvls', 'hybrid', 'ce' or 'sm'")
         if self.fused_forward:
             self.copy_mode = "sm"       # the fused forward kernels do their own fetching
-        if self.copy_mode in ("auto", "nvls"):
+        if self.copy_mode == "auto":
+            self.copy_mode = AUTO_COPY_MODE
+        if self.copy_mode in ("nvls", "hybrid"):
             # every rank must take the same decision: all need a multicast mapping of both arenas
             ok = torch.tensor(
                 [int(self.pub_mc != 0 and self.grad_mc != 0 and self.pub.element_size() == 2)], device=self.device
             )
             dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=dp_group)
-            if bool(ok.item()):
-                self.copy_mode = "nvls"
-            elif self.copy_mode == "nvls":
-                raise RuntimeError(
-                    "DMUON_PEER_COPY=nvls: the symmetric arenas have no NVSwitch multicast mapping on every rank "
-                    "(or the published dtype is not 16-bit)"
-                )
-            else:
+            if not bool(ok.item()):
+                if os.environ.get("DMUON_PEER_COPY", "auto").strip().lower() in ("nvls", "hybrid"):
+                    raise RuntimeError(
+                        f"DMUON_PEER_COPY={self.copy_mode}: the symmetric arenas have no NVSwitch multicast mapping on "
+                        "every rank (or the published dtype is not 16-bit)"
+                    )
                 self.copy_mode = "ce"
+        # which mechanism carries each of the two bulk transfers
+        self.reduce_via = {"nvls": "nvls", "hybrid": "nvls", "ce": "ce", "sm": "sm"}[self.copy_mode]
+        self.publish_via = {"nvls": "nvls", "hybrid": "ce", "ce": "ce", "sm": "sm"}[self.copy_mode]
         for g in groups:
             g._span_by_owner = {}
             for s_, plist in g._pub_by_shard.items():
@@ -359,12 +370,12 @@ class PeerRuntime:
         self._ready_waited_epoch = 0
         self.nvls_publish = nvls_publish_mode()
         self._publish_ticket = None
-        if self.copy_mode == "nvls":
+        if self.reduce_via == "nvls":
             span = max(self.own_hi - self.own_lo, ALIGN)
             self.reduced = torch.zeros(span, dtype=self.grad_dtype, device=self.device)
             # address of arena offset 0 in the reduced copy (only [own_lo, own_hi) is backed)
             self.reduced_base = self.reduced.data_ptr() - self.own_lo * self.grad.element_size()
-        if self.copy_mode == "ce" and self.own_hi > self.own_lo and self.world > 1:
+        if self.reduce_via == "ce" and self.own_hi > self.own_lo and self.world > 1:
             span = self.own_hi - self.own_lo
             self.stage = torch.empty((self.world - 1) * span, dtype=self.grad_dtype, device=self.device)
             gsz = self.grad.element_size()
@@ -479,7 +490,7 @@ class PeerRuntime:
             self._before_owner_writes()
 
     def _before_owner_writes(self) -> None:
-        if self.copy_mode == "nvls":
+        if self.publish_via == "nvls":
             # Owners store straight into every rank's arena, so "consumed" means: this rank has
             # finished every forward / backward that reads the current weights.  That is true at
             # this point of the current stream (the optimizer step or a checkpoint load follows).
@@ -554,7 +565,7 @@ class PeerRuntime:
                     MT.cast(srcs, dsts)
                 else:
                     torch._foreach_copy_(dsts, srcs)
-                if self.copy_mode == "nvls":
+                if self.publish_via == "nvls":
                     # slots that were not multicast during the step (AdamW-routed tensors, the first
                     # publish, a checkpoint load): replicate the local copy to every rank's arena
                     self._multicast_slots(stale)
@@ -571,7 +582,7 @@ class PeerRuntime:
         self._pulled_groups = 0
         for g in self.groups:
             g._pulled_epoch = -1
-        if self._remote_groups == 0 and self.copy_mode != "nvls":
+        if self._remote_groups == 0 and self.publish_via != "nvls":
             # this rank reads nothing from anybody: acknowledge right away
             self._acknowledge_epoch()
 
@@ -585,7 +596,7 @@ class PeerRuntime:
     def _pull_group(self, g: "PeerParamGroup") -> None:
         from ..ops import peer as P
 
-        if self.copy_mode == "nvls":
+        if self.publish_via == "nvls":
             # the owners' stores already put the weights here: only wait (once per epoch and lane)
             # until every owner has announced the epoch
             if self._ready_waited_epoch != self.pub_epoch:
@@ -624,7 +635,7 @@ class PeerRuntime:
         slots = [KIND_PUB_READY * MAX_PEERS + s for s, _, _ in spans]
         live = tuple(p._unsharded_param for p in plist)
         with torch.no_grad(), torch.autograd._unsafe_preserve_version_counter(live):
-            if self.copy_mode == "ce":
+            if self.publish_via == "ce":
                 # one bounded wait for the owners' "published" flags, then copy-engine transfers
                 P.wait_flags(self.flags, KIND_PUB_READY * MAX_PEERS, self.world, self.pub_epoch, self.status)
                 for src, dst, nb in zip(srcs, dsts, nbytes):
@@ -667,7 +678,7 @@ class PeerRuntime:
         from ..ops import peer as P
 
         lane = self.ctx.reduce_lane
-        if self.copy_mode == "nvls":
+        if self.reduce_via == "nvls":
             # one reduce-load per 16 bytes returns the sum over ALL ranks' arenas, formed in the switch:
             # the owner ingests its span once, not once per peer, and keeps a single reduced copy
             lo, hi = g._span_by_owner[self.rank]
@@ -678,7 +689,7 @@ class PeerRuntime:
                 P.multicast_reduce([self.grad_mc + lo * gsz], [self.reduced_base + lo * gsz], [(hi - lo) * gsz],
                                    self.grad_dtype, self.device, blocks_per_tensor=NVLS_REDUCE_BLOCKS)
             return lane.mark()
-        if self.copy_mode == "ce":
+        if self.reduce_via == "ce":
             # gather instead of reduce: bring every peer's slice of this group's owned span into the
             # local staging buffers with copy-engine transfers; the Muon prologue sums them later
             lo, hi = g._span_by_owner[self.rank]
@@ -818,7 +829,7 @@ class PeerParamGroup(DedicatedParamGroup):
                 p._peer_grad_pending = True
                 p.clear_local_grad()
         self._packed_this_step = True
-        if (rt.reduce_mode == "backward" or rt.copy_mode in ("ce", "nvls")) and not self._no_sync:
+        if (rt.reduce_mode == "backward" or rt.reduce_via in ("ce", "nvls")) and not self._no_sync:
             # tell every rank this group's running sum is in the arena, then (as an
             # owner) reduce it on the side lane while backward continues.  A later
             # micro-batch repeats this and overwrites the result with the larger sum.
@@ -830,7 +841,7 @@ class PeerParamGroup(DedicatedParamGroup):
                 self._reduce_ticket = rt.launch_group_reduce(self, owned, self._pack_count)
                 # after a copy-engine gather the sum is still to be done (inside the Muon prologue); after
                 # an in-switch reduce the scale, momentum and cast are
-                self._reduce_owned = owned if rt.copy_mode == "sm" else []
+                self._reduce_owned = owned if rt.reduce_via == "sm" else []
 
     def has_pending_reduce(self) -> bool:
         if self._reduce_ticket is not None:

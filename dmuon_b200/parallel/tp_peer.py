@@ -58,7 +58,8 @@ def tp_peer_possible(device: torch.device, tp_group) -> Optional[str]:
     if dist.get_world_size() > torch.cuda.device_count():
         return "the job spans more than one host"
     try:
-        import torch.distributed._symmetric_memory  # noqa: F401
+        import torch.distributed._symmetric_memory as _symm  # noqa: F401  (an alias: a plain "import torch.x" would
+        # make "torch" a local name of this function and break the lines above)
     except Exception as exc:  # pragma: no cover
         return f"symmetric memory unavailable: {exc}"
     return None
@@ -275,6 +276,7 @@ class TPPeerExchange:
                 p._tp_full_delta = None
                 p._tp_full_grad = None
                 p._reduced_grad = None
+                p._tp_gathered = False
 
     def after_step(self) -> None:
         """End of the optimizer step (current stream, after every prologue):

@@ -253,3 +253,51 @@ def test_three_dimensional_mesh_replicate_shard_tp_matches_single_process():
     for r in range(1, 8):
         for n in sd:
             assert torch.equal(sd[n], res[r][1][n]), (r, n)
+
+
+def _clip_body(rank, world):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+    from torch.distributed.tensor.parallel import ColwiseParallel, RowwiseParallel, parallelize_module
+
+    import dmuon_b200 as dmuon
+
+    mesh = init_device_mesh("cpu", (2, 2), mesh_dim_names=("dp", "tp"))
+    torch.manual_seed(0)
+    model = Net()
+    for blk in model.layers:
+        parallelize_module(blk, mesh["tp"], {"up_proj": ColwiseParallel(), "down_proj": RowwiseParallel()})
+    dmuon.dedicate_params(model, mesh["dp"], _pred, reshard_after_forward=False)
+    for blk in model.layers:
+        fully_shard(blk, mesh=mesh["dp"])
+    fully_shard(model, mesh=mesh["dp"])
+    opt = dmuon.Muon(model, lr=LR, momentum=MU, weight_decay=WD, adamw_lr=ALR, first_step_progress_log=False)
+    dp_rank = mesh["dp"].get_local_rank()
+    out = []
+    for s in range(2):
+        x, y = _data(s)
+        x, y = x[dp_rank * 4 : dp_rank * 4 + 4], y[dp_rank * 4 : dp_rank * 4 + 4]
+        opt.zero_grad()
+        (model(x) - y).pow(2).mean().backward()
+        if s == 1:
+            before = {id(p): opt.state[id(p)]["momentum_buffer"].clone()
+                      for p in dmuon.get_dedicated_params(model) if p.is_owner and p.is_tp_owner}
+            stats = dmuon.clip_grad_norm_(opt, 1e-6)          # coefficient ~1e-6 / norm: the step-2 gradient vanishes
+            assert float(stats.clip_coef) < 1e-3
+        opt.step()
+        if s == 1:
+            for p in dmuon.get_dedicated_params(model):
+                if p.is_owner and p.is_tp_owner:
+                    buf = opt.state[id(p)]["momentum_buffer"]
+                    out.append(((buf - MU * before[id(p)]).abs().max() / before[id(p)].abs().max()).item())
+    return out
+
+
+def test_clipped_tp_gradients_stay_clipped_in_the_step():
+    """Clipping prepares (gathers) the tensor-parallel gradients and scales the
+    gathered matrices; the optimizer step that follows must use those, not
+    gather the unclipped shards a second time.  With a vanishing clip
+    coefficient the momentum after the step is ``mu *`` the old momentum."""
+    res = run_ranks(_clip_body, 4, timeout=300)
+    rel = [v for r in res for v in r]
+    assert len(rel) == 6 and max(rel) < 1e-3, rel

@@ -118,7 +118,10 @@ __global__ void wait_flags_kernel(const DmuonWaitArgs a) {
   block_wait_flags(a.local_flags, a.first, a.count, a.want, a.budget_cycles, a.status);
 }
 
-template <typename TG, typename TM, typename TX>
+// kW: compile-time upper bound of the number of sources (1, 2, 4 or 8).  The per-thread buffer of loads in
+// flight is kW x 8 floats, so the one-source form (a gradient already reduced in the switch) and the
+// two-rank form keep four times the occupancy of the eight-rank form.
+template <typename TG, typename TM, typename TX, int kW>
 __global__ void __launch_bounds__(kBlock) peer_prologue_kernel(const DmuonPeerPrologueArgs a) {
   if (a.ready_flags != nullptr) {
     if (!block_wait_flags(a.ready_flags, 0, a.world, a.ready_want, a.budget_cycles, a.status)) return;
@@ -132,13 +135,13 @@ __global__ void __launch_bounds__(kBlock) peer_prologue_kernel(const DmuonPeerPr
   const float xs = a.xscale ? a.xscale[a.slot[t]] : 1.f;
   const float mu = a.mu;
   const int W = a.world;
-  const TG* g[DMUON_MAX_PEERS];
+  const TG* g[kW];
 #pragma unroll
-  for (int r = 0; r < DMUON_MAX_PEERS; ++r)
+  for (int r = 0; r < kW; ++r)
     g[r] = (r < W) ? reinterpret_cast<const TG*>(a.peer_base[r]) + off : nullptr;
   bool vec = al16(x) && (m == nullptr || al16(m));
 #pragma unroll
-  for (int r = 0; r < DMUON_MAX_PEERS; ++r)
+  for (int r = 0; r < kW; ++r)
     if (r < W) vec = vec && al16(g[r]);
   const long long nvec = vec ? (n / kVec) : 0;
   const long long stride = static_cast<long long>(gridDim.x) * kBlock;
@@ -149,12 +152,12 @@ __global__ void __launch_bounds__(kBlock) peer_prologue_kernel(const DmuonPeerPr
     for (int k = 0; k < kVec; ++k) sum[k] = 0.f;
     // all peer loads are issued before the first use: W independent 16-byte
     // requests in flight per thread
-    float gv[DMUON_MAX_PEERS][kVec];
+    float gv[kW][kVec];
 #pragma unroll
-    for (int r = 0; r < DMUON_MAX_PEERS; ++r)
+    for (int r = 0; r < kW; ++r)
       if (r < W) ld8<TG>(g[r] + i * kVec, gv[r]);
 #pragma unroll
-    for (int r = 0; r < DMUON_MAX_PEERS; ++r)
+    for (int r = 0; r < kW; ++r)
       if (r < W) {
 #pragma unroll
         for (int k = 0; k < kVec; ++k) sum[k] += gv[r][k];
@@ -301,9 +304,20 @@ extern "C" int dmuon_peer_prologue(const DmuonPeerPrologueArgs* a, void* stream_
   long long mx = 0;
   for (int i = 0; i < a->n; ++i) mx = a->numel[i] > mx ? a->numel[i] : mx;
   dim3 grid(grid_x((mx + kVec - 1) / kVec, a->n, a->max_blocks_per_tensor), a->n);
-  DMUON_PEER_DISPATCH(a->grad_dtype, TG,
-    DMUON_PEER_DISPATCH(a->mom_dtype, TM,
-      DMUON_PEER_DISPATCH(a->x_dtype, TX, peer_prologue_kernel<TG, TM, TX><<<grid, kBlock, 0, st>>>(*a))));
+#define DMUON_PEER_PROLOGUE_LAUNCH(KW)                                                                     \
+  DMUON_PEER_DISPATCH(a->grad_dtype, TG,                                                                  \
+    DMUON_PEER_DISPATCH(a->mom_dtype, TM,                                                                 \
+      DMUON_PEER_DISPATCH(a->x_dtype, TX, peer_prologue_kernel<TG, TM, TX, KW><<<grid, kBlock, 0, st>>>(*a))))
+  if (a->world <= 1) {
+    DMUON_PEER_PROLOGUE_LAUNCH(1);
+  } else if (a->world <= 2) {
+    DMUON_PEER_PROLOGUE_LAUNCH(2);
+  } else if (a->world <= 4) {
+    DMUON_PEER_PROLOGUE_LAUNCH(4);
+  } else {
+    DMUON_PEER_PROLOGUE_LAUNCH(8);
+  }
+#undef DMUON_PEER_PROLOGUE_LAUNCH
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }

@@ -466,6 +466,14 @@ class DedicatedParamGroup:
                     by_group[id(p.tp_group)].append(p)
                 for gid, plist in by_group.items():
                     exchanges[gid].publish_shards(plist)
+        if todo:
+            # gathers and scatters use ONE communicator from two lanes; when the optimizer works through
+            # the groups block by block, a later block's gather is issued while an earlier block's scatter
+            # is in flight.  Collectives of one communicator must not overlap, and every rank must run them
+            # in the same order: order this gather after whatever the scatter lane has been given so far
+            # (tp_scatter_delta orders the scatter after the gathers in the same way).
+            lane.follow(self.comm_ctx.replicate_broadcast_lane)
+            lane.follow(self.comm_ctx.broadcast_lane)       # the scatter lane of the replicated placement
         with lane.use(), torch.no_grad():
             with record_function(f"dmuon.tp_gather.{self.name}"):
                 for p in todo:

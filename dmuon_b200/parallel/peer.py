@@ -20,13 +20,15 @@ Newton-Schulz batch, or by the last Newton-Schulz GEMM's own epilogue -- so they
 land in every rank's arena and readers copy nothing; gradients are summed inside
 the switch: per layer, during backward, a small kernel on the reduce lane reads
 the owner's span through the multicast mapping with ``multimem.ld_reduce`` and
-keeps ONE reduced copy, which the Muon prologue then reads locally.  "hybrid"
-(what "auto" picks where the mapping exists): that in-switch reduce, with the
-publish left to the readers' copy engines.  "ce": copy-engine transfers.  Readers pull publish spans with asynchronous
-copies, owners gather the peers' gradient slices of each layer into local
-staging buffers while backward is still running, and the fixed-order fp32 sum
-runs locally inside the Muon prologue; no SM is taken from the forward and
-backward GEMMs.  "sm": the pull and reduce kernels load through the peer
+keeps ONE reduced copy, which the Muon prologue then reads locally.  "hybrid":
+that in-switch reduce, with the publish left to the readers' copy engines (the
+owner keeps one reduced copy instead of N - 1 staged slices: 6.7 GiB less at
+four ranks of an 8B model).  "ce" (what "auto" picks: the fastest step measured
+at two and at four ranks): copy-engine transfers.  Readers pull publish spans
+with asynchronous copies, owners gather the peers' gradient slices of each layer
+into local staging buffers while backward is still running, and the fixed-order
+fp32 sum runs locally inside the Muon prologue; no SM is taken from the forward
+and backward GEMMs.  "sm": the pull and reduce kernels load through the peer
 mappings themselves (the form the fused forward GEMM builds on).
 
 Ordering uses four monotonically increasing epoch words per rank in a
@@ -65,11 +67,11 @@ NVLS_REDUCE_BLOCKS = 16
 NVLS_PUBLISH_BLOCKS = 16
 
 
-#: what ``DMUON_PEER_COPY=auto`` means.  "hybrid": gradients are summed inside the NVSwitch
-#: (``multimem.ld_reduce``: one reduced copy on the owner instead of N - 1 staged slices, the prologue reads
-#: 1/N of the bytes), weights are pulled by the readers' copy engines during forward (which costs the
-#: optimizer step nothing).  Falls back to "ce" where the arenas have no multicast mapping.
-AUTO_COPY_MODE = "hybrid"
+#: what ``DMUON_PEER_COPY=auto`` means.  Copy engines for both bulk transfers: on Llama-3-8B the step took
+#: 487.6 ms at four ranks against 494.2 ms ("hybrid": in-switch reduce, copy-engine publish) and 496.2 ms
+#: ("nvls"), because the in-switch reduce and the multicast stores take SMs from backward and from the
+#: Newton-Schulz products while the copy engines take none.  "hybrid" holds 6.7 GiB less on the owner.
+AUTO_COPY_MODE = "ce"
 
 
 def nvls_publish_mode() -> str:

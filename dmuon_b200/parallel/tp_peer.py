@@ -146,7 +146,8 @@ class TPPeerExchange:
         self.status = G.status_buffer(self.device)
         self.gather_epoch = 0         # gather calls issued so far (same number on every rank of the group)
         self.scatter_epoch = 0
-        self._grad_consumed_waited = -1
+        self._grad_waited_this_step = False
+        self._gather_epoch_at_step_start = 0
         self._delta_waited_this_step = False
         self._gathered_since_step = False
         dist.barrier(group=tp_group)
@@ -170,10 +171,11 @@ class TPPeerExchange:
         from ..ops import multi_tensor as MT
 
         with record_function(f"dmuon.tp_peer.publish_shards.params{len(dparams)}"):
-            if self._grad_consumed_waited != self.gather_epoch:
-                # first gather after an optimizer step: the owners must be done reading the old shards
-                self._wait_all(KIND_GRAD_CONSUMED, self.gather_epoch)
-                self._grad_consumed_waited = self.gather_epoch
+            if not self._grad_waited_this_step:
+                # first gather after an optimizer step: the owners must be done reading the shards of the
+                # step before (they announce that once, with the number of gathers that step had reached)
+                self._wait_all(KIND_GRAD_CONSUMED, self._gather_epoch_at_step_start)
+                self._grad_waited_this_step = True
             srcs, dsts = [], []
             for p in dparams:
                 g = p._reduced_grad
@@ -285,6 +287,8 @@ class TPPeerExchange:
             self._signal(KIND_GRAD_CONSUMED, self.gather_epoch)
             self._gathered_since_step = False
         self._delta_waited_this_step = False
+        self._grad_waited_this_step = False
+        self._gather_epoch_at_step_start = self.gather_epoch
 
     def check(self) -> None:
         from ..ops import gemm as G

@@ -9,10 +9,11 @@ from dist_utils import run_ranks
 pytestmark = pytest.mark.gpu
 
 
-def _body(rank, world, use_peer, clip, steps):
+def _body(rank, world, use_peer, clip, steps, single_pass=True):
     import os
 
     os.environ["DMUON_TP_PEER"] = "1" if use_peer else "0"
+    os.environ["DMUON_NS_SINGLE_PASS"] = "1" if single_pass else "0"      # read when the kernels' module is imported
     import torch.distributed as dist
     from torch.distributed.device_mesh import init_device_mesh
     from torch.distributed.fsdp import fully_shard
@@ -44,40 +45,75 @@ def _body(rank, world, use_peer, clip, steps):
     ctx = model._dedicated_comm_ctx
     assert bool(ctx.tp_exchanges) == use_peer
     g = torch.Generator().manual_seed(31 + mesh["dp"].get_local_rank())      # TP peers see the same batch
-    losses = []
+    losses, first = [], None
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+
     for _ in range(steps):
-        ids = torch.randint(0, cfg.vocab_size, (2, 65), generator=g).to(dev)
+        # 512 tokens: the 256-wide matrices get full-rank gradients (Newton-Schulz amplifies rounding noise
+        # along the null directions of a rank-deficient one); matmul attention: its backward has no atomics,
+        # so the two runs that are compared see the same gradients
+        ids = torch.randint(0, cfg.vocab_size, (4, 129), generator=g).to(dev)
         opt.zero_grad()
-        loss = model(ids[:, :-1], labels=ids[:, 1:])
-        loss.backward()
+        with sdpa_kernel(SDPBackend.MATH):
+            loss = model(ids[:, :-1], labels=ids[:, 1:])
+            loss.backward()
         if clip:
             dmuon.clip_grad_norm_(opt, 0.5)
         opt.step()
+        if first is None:
+            first = {k: v for k, v in dmuon.get_model_state_dict(model, rank0_only=False).items() if "proj" in k}
         lt = loss.detach().float().clone()
         dist.all_reduce(lt)
         losses.append(float(lt) / world)
     for ex in ctx.tp_exchanges.values():
         ex.check()
     sd = dmuon.get_model_state_dict(model, rank0_only=False)
-    return losses, {k: v for k, v in sd.items() if "proj" in k}
+    return losses, {k: v for k, v in sd.items() if "proj" in k}, first
+
+
+def _rel(a: dict, b: dict) -> dict:
+    return {k: (a[k].float() - v.float()).norm().item() / (v.float().norm().item() + 1e-12) for k, v in b.items()}
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 @pytest.mark.parametrize("clip", [False, True])
 def test_tp_gather_scatter_over_peer_memory_matches_collectives(clip):
-    """Row- and column-sharded matrices, DP x TP = (1 or 2) x 2: the peer-memory
-    path gives the collective path's weights (the only difference is the order
-    in which the shards' sums of squares are added up)."""
+    """Row- and column-sharded matrices, DP x TP = (1 or 2) x 2, peer-memory
+    path against the collective path.
+
+    The two paths differ only in the order in which the shards' sums of squares
+    are added (atomics: the order is not even fixed within one path).  Where
+    the sum comes out the same, the weights after one step agree to the last
+    bit or two; where it differs in the last bit, another fp16 rounding of the
+    Newton-Schulz operand follows, and the fp16 Gram iteration turns that into
+    a visible difference along the gradient's weak singular directions (they
+    sit below fp16's resolution of the Gram matrix; on this model up to 4 % of
+    a square matrix after three steps).  How large "visible" is gets measured,
+    not assumed: the collective path is run once more with the other, equally
+    valid operand rounding (two-pass instead of single-pass cast), and the peer
+    path has to stay within a small multiple of that distance -- and, without
+    clipping (a clip coefficient reaches every matrix), at least half of the
+    matrices must agree to 1e-6 after the first step, which only holds if every
+    shard lands where it belongs on the way in and on the way out."""
     world = 4 if torch.cuda.device_count() >= 4 else 2
     ref = run_ranks(_body, world, args=(False, clip, 3), backend="nccl", timeout=600)
+    alt = run_ranks(_body, world, args=(False, clip, 3, False), backend="nccl", timeout=600)
     got = run_ranks(_body, world, args=(True, clip, 3), backend="nccl", timeout=600)
     for a, b in zip(got[0][0], ref[0][0]):
         assert abs(a - b) < 1e-2 * max(1.0, abs(b)), (got[0][0], ref[0][0])
-    # two separate runs do not see bit-identical gradients (attention backward uses atomics) and
-    # Newton-Schulz amplifies such differences along weak singular directions: a norm-wise bound
-    for k, v in ref[0][1].items():
-        rel = (got[0][1][k].float() - v.float()).norm().item() / (v.float().norm().item() + 1e-12)
-        assert rel < 3e-2, (k, rel)
+    one = _rel(got[0][2], ref[0][2])
+    noise = _rel(alt[0][1], ref[0][1])
+    three = _rel(got[0][1], ref[0][1])
+    fmt = lambda d: {k.replace("layers.", "").replace(".weight", ""): f"{r:.1e}" for k, r in d.items()}  # noqa: E731
+    print("after one step, peer vs collective:", fmt(one))
+    print("after three steps, collective vs collective with the other operand rounding:", fmt(noise))
+    print("after three steps, peer vs collective:", fmt(three))
+    if not clip:
+        exact = sum(1 for r in one.values() if r < 1e-6)
+        assert 2 * exact >= len(one), one
+    for k in three:
+        assert one[k] < 3.0 * noise[k] + 5e-3, (k, one[k], noise[k])
+        assert three[k] < 3.0 * noise[k] + 5e-3, (k, three[k], noise[k])
     # every rank reports the same full tensors
     for k, v in got[0][1].items():
         assert torch.equal(v, got[-1][1][k]), k

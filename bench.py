@@ -224,6 +224,9 @@ def make_mesh(args, world):
 def _plane_name(ctx) -> str:
     rt = getattr(ctx, "peer_runtime", None)
     if rt is None:
+        if getattr(ctx, "tp_exchanges", None):
+            return ("nccl on the data-parallel axis; tensor-parallel shards read in place over peer memory by the "
+                    "Muon prologue, update slices pulled and applied by one kernel")
         return "nccl"
     reduce = {
         "nvls": "gradients summed in the switch per layer during backward (multimem.ld_reduce), one reduced copy read by the Muon prologue kernel",
@@ -627,6 +630,7 @@ def run(args):
                 "model_ops": ("n/a" if (args.impl != "ours" or args.model_impl == "hf") else
                               "plain PyTorch" if args.plain_model_ops else "fused SwiGLU / RoPE / linear-cross-entropy kernels"),
                 "activation_checkpointing": bool(args.act_ckpt),
+                "clip_norm": (float(args.clip_norm) if float(args.clip_norm) > 0 else None),
                 "l2": "per-step working set (weights + activations, tens of GB) is far larger than the 126 MB L2",
             },
         }

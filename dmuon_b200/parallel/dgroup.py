@@ -537,7 +537,12 @@ class DedicatedParamGroup:
                             p._tp_scatter_recv = recv
                     lane.keep_alive(recv)
                     if p.is_tp_owner:
+                        # the update was produced on the compute stream and is read here, on the scatter lane,
+                        # by the cast / the column-shard copies below; it is dropped at the end of this loop
+                        # body, so the allocator must learn that this lane still uses it
+                        lane.keep_alive(p._tp_full_delta)
                         delta = p._tp_full_delta.to(p._owned_data.dtype)
+                        lane.keep_alive(delta)
                         pieces = [c.contiguous() for c in delta.chunk(p.tp_group.size(), dim=p.shard_dim)]
                         for c in pieces:
                             lane.keep_alive(c)

@@ -254,8 +254,11 @@ class TPPeerExchange:
                     if d is None:
                         raise RuntimeError(f"{p.fqn}: the TP owner has no update to scatter")
                     if d.data_ptr() != view.data_ptr():
-                        # produced outside the buffer (PyTorch Newton-Schulz path)
+                        # produced outside the buffer (PyTorch Newton-Schulz path), on the compute stream;
+                        # it is dropped below while this copy may still be queued on the scatter lane
                         self.before_delta_writes()
+                        if d.is_cuda:
+                            d.record_stream(torch.cuda.current_stream(d.device))
                         view.copy_(d.reshape(view.shape))
             self.scatter_epoch += 1
             self._signal(KIND_DELTA_READY, self.scatter_epoch)

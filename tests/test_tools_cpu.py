@@ -60,3 +60,26 @@ def test_trace_analysis_without_gpu_events_still_lists_ranges():
     s = at.analyze([{"ph": "X", "cat": "user_annotation", "name": "dmuon.peer.publish_owned", "ts": 1.0, "dur": 2000.0}])
     assert s["gpu_events"] == 0 and s["ranges"]["dmuon.peer.publish_owned"]["count"] == 1
     assert "no GPU events" in at.format_report(s)
+
+
+def test_ownership_benchmark_arms_follow_the_same_trajectory():
+    """``benchmarks/bench_e2e.py`` on two gloo ranks: plain FSDP2 with every rank
+    orthogonalising the all-gathered gradient (no ownership, nothing of this
+    package's placement code) and dedicated ownership must reach the same loss --
+    an end-to-end oracle that shares only the model and the Newton-Schulz function."""
+    import subprocess
+    import sys
+
+    cmd = [
+        sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+        "--master-port", "29641", str(ROOT / "benchmarks" / "bench_e2e.py"), "--cpu", "--arms", "redundant,owned",
+        "--layers", "2", "--width", "128", "--heads", "4", "--vocab", "512", "--batch", "2", "--seq", "64",
+        "--steps", "3", "--warmup", "1",
+    ]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    recs = [json.loads(line) for line in out.stdout.splitlines() if line.startswith("{")]
+    arms = {r["arm"]: r for r in recs if "arm" in r}
+    assert set(arms) == {"redundant", "owned"}
+    assert abs(arms["redundant"]["loss"] - arms["owned"]["loss"]) < 2e-3, arms
+    assert any(r.get("summary") and "owned_vs_redundant_speedup" in r for r in recs)

@@ -92,12 +92,13 @@ class _ModelIndex:
             yield self.model.get_submodule(path) if path else self.model
 
     def layer_module(self, p: nn.Parameter) -> nn.Module:
-        """The ``layers.N`` / ``blocks.N`` ancestor, else the direct parent."""
+        """The ``layers.N`` / ``blocks.N`` / ``h.N`` / ``layer.N`` ancestor (the
+        usual names of a model's repeated block list), else the direct parent."""
         parent, _ = self.parent(p)
         fqn = self.module_fqn[id(parent)]
         parts = fqn.split(".") if fqn else []
         for i in range(len(parts) - 1):
-            if parts[i] in ("layers", "blocks"):
+            if parts[i] in ("layers", "blocks", "h", "layer") and parts[i + 1].isdigit():
                 try:
                     return self.model.get_submodule(".".join(parts[: i + 2]))
                 except AttributeError:

@@ -127,3 +127,20 @@ def load() -> ctypes.CDLL:
 
 def is_loaded() -> bool:
     return _lib is not None
+
+
+def _main() -> int:
+    """``python -m dmuon_b200.ops.build [--force] [--verbose]``: compile the kernel library in place."""
+    import argparse
+
+    ap = argparse.ArgumentParser(description="Compile dmuon_b200's CUDA sources for sm_100a into the package.")
+    ap.add_argument("--force", action="store_true", help="rebuild even if the library is up to date")
+    ap.add_argument("--verbose", action="store_true", help="print ptxas resource usage (registers, spills, shared memory)")
+    args = ap.parse_args()
+    path = build(force=args.force, verbose=args.verbose)
+    print(path)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(_main())

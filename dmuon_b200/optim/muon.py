@@ -972,6 +972,19 @@ class Muon(torch.optim.Optimizer):
     def last_muon_grad_clip_stats(self):
         return self._last_clip_stats
 
+    def scale_grads_on_next_step(self, coef) -> None:
+        """Multiply EVERY gradient of the next ``step()`` by ``coef`` (a float or a
+        one-element tensor on the optimizer's device) inside the kernels that
+        read the gradients anyway -- the Muon prologue and the AdamW passes --
+        instead of in a separate pass over all gradients.  Meant for trainers
+        that compute one global clip coefficient themselves (loss-scale
+        unscaling, a norm over several models): ``opt.scale_grads_on_next_step
+        (coef); opt.step()`` equals scaling all gradients by ``coef`` first.  The
+        coefficient is used once; several calls before a step multiply."""
+        t = coef if torch.is_tensor(coef) else torch.tensor(float(coef), dtype=torch.float32, device=self.device)
+        t = t.detach().reshape(()).to(device=self.device, dtype=torch.float32)
+        self._pending_gscale = t if self._pending_gscale is None else self._pending_gscale * t
+
     def consume_last_step_profile(self) -> Optional[dict]:
         prof, self._last_profile = self._last_profile, None
         return None if prof is None else prof.summary()

@@ -288,3 +288,54 @@ def test_broadcast_load_carries_buffers_and_skips_missing_keys_on_every_rank():
         assert torch.equal(running, torch.arange(16.0))
     # the absent matrix kept its initial value, identically on both ranks
     assert torch.equal(res[0][0]["b_proj.weight"], res[1][0]["b_proj.weight"])
+
+
+def _scaled_step_body(rank, world, how):
+    """One step with every gradient multiplied by 0.25: through the loss ("loss"),
+    through ``scale_grads_on_next_step`` ("defer", twice 0.5), or not at all ("none")."""
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+    from test_e2e_cpu import HP, _build_model, _data, _pred
+
+    mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("dp",))
+    model = _build_model()
+    dmuon.dedicate_params(model, mesh, _pred, reshard_after_forward=False)
+    for layer in model.layers:
+        fully_shard(layer, mesh=mesh)
+    fully_shard(model, mesh=mesh)
+    opt = dmuon.Muon(model, lr=HP["lr"], adamw_lr=HP["adamw_lr"], weight_decay=HP["weight_decay"],
+                     momentum=HP["momentum"], adamw_weight_decay=HP["adamw_wd"], adamw_eps=1e-3,
+                     first_step_progress_log=False)
+    x, y = _data(0)
+    per = 4 // world
+    x, y = x[rank * per : (rank + 1) * per], y[rank * per : (rank + 1) * per]
+    loss = model(x, labels=y)
+    (loss * 0.25 if how == "loss" else loss).backward()
+    if how == "defer":
+        opt.scale_grads_on_next_step(0.5)
+        opt.scale_grads_on_next_step(torch.tensor(0.5))      # several calls multiply
+    opt.step()
+    assert opt._pending_gscale is None                       # used once
+    sd = dmuon.get_model_state_dict(model, rank0_only=False)
+    moms = {dp.fqn: opt.state[id(dp)]["momentum_buffer"].clone() for dp in opt.owned_muon_params()}
+    return sd, moms
+
+
+def test_deferred_gradient_scale_equals_scaling_the_loss():
+    """``scale_grads_on_next_step(c)`` + ``step()`` gives what scaling every gradient
+    by ``c`` gives: the Muon momentum buffers are ``c`` times the unscaled ones, and
+    all weights (Muon and AdamW with a large eps, which makes AdamW scale-sensitive)
+    equal those of a run whose loss was multiplied by ``c``."""
+    a = run_ranks(_scaled_step_body, 2, args=("loss",))
+    b = run_ranks(_scaled_step_body, 2, args=("defer",))
+    c = run_ranks(_scaled_step_body, 2, args=("none",))
+    for r in range(2):
+        for k, v in a[r][0].items():
+            assert (b[r][0][k].float() - v.float()).abs().max().item() < 1e-6, k
+        for k, m in c[r][1].items():
+            assert torch.allclose(b[r][1][k], 0.25 * m, atol=1e-7, rtol=1e-5), k
+    # and it is not a no-op: AdamW-routed weights differ from the unscaled run
+    diff = max((b[0][0][k].float() - c[0][0][k].float()).abs().max().item() for k in c[0][0] if "proj" not in k)
+    assert diff > 1e-6

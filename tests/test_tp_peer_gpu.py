@@ -9,7 +9,7 @@ from dist_utils import run_ranks
 pytestmark = pytest.mark.gpu
 
 
-def _body(rank, world, use_peer, clip, steps, single_pass=True):
+def _body(rank, world, use_peer, clip, steps, single_pass=True, torch_ns=False):
     import os
 
     os.environ["DMUON_TP_PEER"] = "1" if use_peer else "0"
@@ -41,7 +41,11 @@ def _body(rank, world, use_peer, clip, steps, single_pass=True):
     for layer in model.layers:
         fully_shard(layer, mesh=mesh["dp"])
     fully_shard(model, mesh=mesh["dp"])
-    opt = dmuon.Muon(model, lr=0.02, adamw_lr=1e-3, weight_decay=0.1, first_step_progress_log=False)
+    extra = {}
+    if torch_ns:
+        # fp32 PyTorch Newton-Schulz: no fp16 rounding to amplify, so the two transports must agree tightly
+        extra["ns_backend"] = dmuon.NewtonSchulz(kernel="torch", compute_dtype=torch.float32)
+    opt = dmuon.Muon(model, lr=0.02, adamw_lr=1e-3, weight_decay=0.1, first_step_progress_log=False, **extra)
     ctx = model._dedicated_comm_ctx
     assert bool(ctx.tp_exchanges) == use_peer
     g = torch.Generator().manual_seed(31 + mesh["dp"].get_local_rank())      # TP peers see the same batch
@@ -117,3 +121,18 @@ def test_tp_gather_scatter_over_peer_memory_matches_collectives(clip):
     # every rank reports the same full tensors
     for k, v in got[0][1].items():
         assert torch.equal(v, got[-1][1][k]), k
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tp_peer_exchange_is_exact_when_newton_schulz_runs_in_fp32():
+    """With the fp32 PyTorch iteration nothing amplifies last-bit differences, and
+    the peer path then only moves bytes (shards copied into the symmetric buffer,
+    assembled by the gather kernel, the update copied into the owner's slot, slices
+    pulled and applied): weights must match the collective path to rounding, with
+    clipping in the loop (its norm is summed in another order)."""
+    world = 4 if torch.cuda.device_count() >= 4 else 2
+    ref = run_ranks(_body, world, args=(False, True, 3, True, True), backend="nccl", timeout=600)
+    got = run_ranks(_body, world, args=(True, True, 3, True, True), backend="nccl", timeout=600)
+    worst = _rel(got[0][1], ref[0][1])
+    print("fp32 Newton-Schulz, peer vs collective after three steps:", {k: f"{r:.1e}" for k, r in worst.items()})
+    assert max(worst.values()) < 3e-4, worst

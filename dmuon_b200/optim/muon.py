@@ -926,6 +926,14 @@ class Muon(torch.optim.Optimizer):
             st = self._adamw_state(id(dp), p, dp._optim_dtype)
             entries.append((p, g.reshape(p.shape), st, None))
         self._adamw_apply(entries, pg, gscale)
+        if self.device.type == "cuda":
+            # reduced gradients may have been allocated on the reduce lane; the AdamW kernels above read them on
+            # this stream, so tell the allocator before the references are dropped (the lanes also wait for this
+            # stream before they allocate again; this makes the lifetime independent of that)
+            cur = torch.cuda.current_stream(self.device)
+            for _, g, _, _ in entries:
+                if g.is_cuda:
+                    g.record_stream(cur)
         for dp in bucket:
             dp._reduced_grad = None
             dp._sharded_adamw_grad = None

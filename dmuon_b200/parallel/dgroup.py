@@ -502,6 +502,11 @@ class DedicatedParamGroup:
             self._tp_gather_ticket = None
         for p, parts in self._tp_gather_keep:
             p._tp_full_grad = torch.cat(parts, dim=p.shard_dim)
+            if parts and parts[0].is_cuda:
+                # the parts were allocated on the gather lane and are read here, on the current stream
+                cur = torch.cuda.current_stream(self.device)
+                for t in parts:
+                    t.record_stream(cur)
         self._tp_gather_keep = []
 
     def tp_scatter_delta(self, lane: Optional[Lane] = None) -> Optional[Ticket]:

@@ -590,7 +590,6 @@ def dedicate_params_ddp(
     hook_boundary_strict: bool = True,
     hook_boundary_resolver=None,
     assignment_group_key_fn=None,
-    route_hint_fn=None,
     max_owners_per_group: Optional[int] = None,
     owner_strategy: Optional[str] = None,
     owner_cost_model: Optional[str] = None,
@@ -599,6 +598,7 @@ def dedicate_params_ddp(
     param_policy_fn=None,
     process_group_policy: Optional[str] = None,
     comm_backend: Optional[str] = None,
+    route_hint_fn=None,
 ) -> dict:
     """Replicated (DDP-style) placement: every rank keeps the live parameter,
     gradients are reduced to the owner, the owner's update is broadcast after
@@ -645,7 +645,6 @@ def dedicate_params_ddp_tp(
     hook_boundary_strict: bool = True,
     hook_boundary_resolver=None,
     assignment_group_key_fn=None,
-    route_hint_fn=None,
     max_owners_per_group: Optional[int] = None,
     owner_strategy: Optional[str] = None,
     owner_cost_model: Optional[str] = None,
@@ -654,6 +653,7 @@ def dedicate_params_ddp_tp(
     param_policy=None,
     param_policy_fn=None,
     process_group_policy: Optional[str] = None,
+    route_hint_fn=None,
 ) -> dict:
     """Replicated placement for models whose matrices are DTensors sharded on a
     tensor-parallel mesh dimension (``mesh`` is the data-parallel dimension)."""

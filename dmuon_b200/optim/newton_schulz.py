@@ -267,14 +267,27 @@ def gram_newton_schulz_distributed_local(
     ).squeeze(0)
 
 
-def newton_schulz(G: Tensor, steps: int = 5, backend: str = "gram", **kwargs) -> Tensor:
-    """Orthogonalise ``G`` with the default coefficients; ``backend`` is
+def newton_schulz(
+    G: Tensor,
+    steps: int = 5,
+    eps: float = 1e-7,
+    coefficients: Optional[Sequence[Sequence[float]]] = None,
+    restart_iterations: Optional[Sequence[int]] = None,
+    backend: str = "gram",
+    **kwargs,
+) -> Tensor:
+    """Orthogonalise ``G`` with the default coefficients (positional arguments
+    as in the reference, dmuon/optim/newton_schulz.py:299); ``backend`` is
     ``"gram"`` or ``"direct"``."""
     if backend == "gram":
-        return gram_newton_schulz(G, steps=steps, **kwargs)
+        return gram_newton_schulz(G, steps=steps, eps=eps, coefficients=coefficients,
+                                  restart_iterations=restart_iterations, **kwargs)
     if backend == "direct":
-        return direct_newton_schulz(G, steps=steps, **kwargs)
+        return direct_newton_schulz(G, steps=steps, eps=eps, coefficients=coefficients, **kwargs)
     raise ValueError(f"backend must be 'gram' or 'direct', got {backend!r}")
+
+
+gram_newton_schulz_local = gram_newton_schulz      # alias kept by the reference (dmuon/optim/newton_schulz.py:779)
 
 
 class NewtonSchulz:

@@ -180,8 +180,37 @@ class DedicatedCommContext:
             return contextlib.nullcontext()
         return _TimedRegion(self, kind, group_name, phase, lane)
 
-    def drain_profile(self, kind: str = "forward") -> dict:
-        """Aggregate finished timers; unfinished ones stay queued."""
+    # names of the reference's context (dmuon/_core/comm.py: record_* / consume_*), for code that feeds or reads
+    # the profile directly
+    def record_forward_unshard_counter(self, group_name: str, **values: int) -> None:
+        for key, inc in values.items():
+            self._profile_counts[group_name][key] += int(inc)
+
+    def _record_event(self, kind: str, group_name: str, phase: str, start, end, nbytes: int, **flags) -> None:
+        self._profile_events[kind].append({"group": group_name, "phase": phase, "start": start, "end": end})
+        if nbytes:
+            self._profile_counts[group_name][f"{phase}_bytes"] += int(nbytes)
+        for key, on in flags.items():
+            if on:
+                self._profile_counts[group_name][f"{phase}_{key}_calls"] += 1
+
+    def record_forward_unshard_event(self, *, group_name: str, phase: str, start, end, bytes: int = 0,
+                                     prefetch: bool = False) -> None:
+        """Queue a finished-or-pending CUDA-event pair of the forward publish."""
+        self._record_event("forward", group_name, phase, start, end, bytes, prefetch=prefetch)
+
+    def record_post_step_event(self, *, group_name: str, phase: str, start, end, bytes: int = 0) -> None:
+        self._record_event("post_step", group_name, phase, start, end, bytes)
+
+    def consume_forward_unshard_profile(self, *, clear: bool = True) -> dict:
+        return self.drain_profile("forward", clear=clear)
+
+    def consume_post_step_profile(self, *, clear: bool = True) -> dict:
+        return self.drain_profile("post_step", clear=clear)
+
+    def drain_profile(self, kind: str = "forward", clear: bool = True) -> dict:
+        """Aggregate finished timers; unfinished ones stay queued.  With
+        ``clear=False`` the finished ones and the counters are kept as well."""
         events = self._profile_events[kind]
         summary: dict[str, dict[str, float]] = defaultdict(lambda: defaultdict(float))
         pending = []
@@ -193,11 +222,13 @@ class DedicatedCommContext:
                 slot[f"{rec['phase']}_calls"] += 1
             else:
                 pending.append(rec)
-        self._profile_events[kind] = pending
+        if clear:
+            self._profile_events[kind] = pending
         out = {g: dict(v) for g, v in summary.items()}
         for g, counts in self._profile_counts.items():
             out.setdefault(g, {}).update({k: int(v) for k, v in counts.items()})
-        self._profile_counts.clear()
+        if clear:
+            self._profile_counts.clear()
         return out
 
 

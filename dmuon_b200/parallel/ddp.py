@@ -106,7 +106,12 @@ def replicate(model: nn.Module, mesh=None) -> nn.Module:
     return model
 
 
-def replicate_tp(model: nn.Module, dp_mesh) -> nn.Module:
-    """Tensor-parallel variant: ``dp_mesh`` is the data-parallel sub-mesh; the
-    gradients' local shards are averaged over it."""
-    return replicate(model, dp_mesh)
+def replicate_tp(model: nn.Module, mesh=None, *, dp_mesh=None) -> nn.Module:
+    """Tensor-parallel variant: ``mesh`` is the data-parallel sub-mesh (keyword
+    ``dp_mesh`` is accepted as well); the gradients' local shards are averaged
+    over it."""
+    if mesh is None:
+        mesh = dp_mesh
+    if mesh is None:
+        raise TypeError("replicate_tp needs the data-parallel mesh")
+    return replicate(model, mesh)

@@ -34,6 +34,9 @@ def iter_states(model: nn.Module) -> Iterator:
         yield from ctx.all_states
 
 
+iter_dedicated_states = iter_states        # the reference's name (dmuon/utils.py:28)
+
+
 def iter_groups(model: nn.Module) -> Iterator:
     """Groups in forward (module registration) order -- identical on every rank."""
     for st in iter_states(model):
@@ -44,8 +47,16 @@ def get_dedicated_params(model: nn.Module) -> list:
     return [p for g in iter_groups(model) for p in g.params]
 
 
-def get_owned_params(model: nn.Module) -> list:
-    return [p for p in get_dedicated_params(model) if p.is_owner]
+def get_owned_params(model: nn.Module, rank=None) -> list:
+    """Dedicated parameters owned by this rank, or -- with ``rank`` (a shard
+    index or a ``(shard, replicate)`` coordinate, as in the reference's
+    ``get_owned_params(model, rank)``) -- by that owner coordinate."""
+    if rank is None:
+        return [p for p in get_dedicated_params(model) if p.is_owner]
+    from ..parallel.topology import normalize_owner_rank
+
+    want = tuple(normalize_owner_rank(rank))
+    return [p for p in get_dedicated_params(model) if tuple(p.owner_rank) == want]
 
 
 # --------------------------------------------------------------------------- gradients
@@ -67,11 +78,15 @@ def wait_group_muon_grads(group) -> None:
     group.materialize_tp_grads()
 
 
-def prepare_muon_grads(model: nn.Module, coalesce_wait: bool = False) -> None:
-    """Make every owned gradient ready on the current stream."""
+def prepare_muon_grads(model: nn.Module, coalesce_wait: bool = False, *, use_reduce_stream: Optional[bool] = None) -> None:
+    """Make every owned gradient ready on the current stream.
+    ``use_reduce_stream`` (keyword of the reference's function): ``False`` drains
+    the reduces on the current stream instead of on the reduce lane; the default
+    here is the lane, which is what the optimizer uses."""
     groups = list(iter_groups(model))
+    on_lane = True if use_reduce_stream is None else bool(use_reduce_stream)
     for g in groups:
-        prepare_group_muon_grads(g, use_reduce_lane=True)
+        prepare_group_muon_grads(g, use_reduce_lane=on_lane)
     if coalesce_wait and groups:
         # one aggregate wait on the lane instead of one per group
         groups[0].comm_ctx.reduce_lane.mark().wait_on_current()
@@ -109,11 +124,15 @@ def wait_all_replicate_broadcasts(model: nn.Module) -> None:
 wait_all_post_step_broadcasts = wait_all_replicate_broadcasts
 
 
-def collect_forward_unshard_profile(model: nn.Module) -> dict:
+def collect_forward_unshard_profile(model: nn.Module, *, clear: bool = True, synchronize: bool = False) -> dict:
     """Aggregated CUDA-event timings and counters of the forward publish
-    (enabled with ``DMUON_RECORD_FORWARD_PROFILE=1``)."""
+    (enabled with ``DMUON_RECORD_FORWARD_PROFILE=1``).  ``synchronize=True``
+    waits for the device first, so that no timer is still pending;
+    ``clear=False`` leaves the records in place for a later call."""
     ctx = get_comm_ctx(model)
-    return ctx.drain_profile("forward")
+    if synchronize and ctx.device.type == "cuda":
+        torch.cuda.synchronize(ctx.device)
+    return ctx.drain_profile("forward", clear=clear)
 
 
 def collect_post_step_profile(model: nn.Module) -> dict:

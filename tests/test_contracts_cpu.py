@@ -5,6 +5,8 @@ from types import SimpleNamespace
 import pytest
 import torch
 
+from dist_utils import run_ranks
+
 
 def _fake_muon(backend="gram", policy="beneficial", ratio=0.5, restarts=(2,)):
     from dmuon_b200.optim.muon import Muon
@@ -126,3 +128,78 @@ def test_bucket_clip_handles_non_contiguous_and_non_finite_gradients():
     )
     assert bool(res.stats_by_name["bad"].found_inf) and not bool(res.stats_by_name["fine"].found_inf)
     assert not bool(res.stats_by_name["fine"].clipped) and float(fine[1]) == 4.0
+
+
+def _diag_body(rank, world):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+    from test_e2e_cpu import _build_model, _pred
+
+    mesh = init_device_mesh("cpu", (2, world // 2), mesh_dim_names=("replicate", "shard"))
+    model = _build_model()
+    dmuon.dedicate_params(model, mesh["shard"], _pred, replicate_mesh=mesh["replicate"])
+    for layer in model.layers:
+        fully_shard(layer, mesh=mesh)
+    fully_shard(model, mesh=mesh)
+    opt = dmuon.Muon(model, first_step_progress_log=False)
+    pg = dmuon.summarize_param_groups(model, opt, max_rows=5)
+    assert pg == dmuon.summarize_param_groups(opt, max_rows=5)            # single-argument form
+    plan = dmuon.summarize_comm_plan(model, max_groups=2, max_params_per_group=3)
+    owned_here = dmuon.get_owned_params(model)
+    coord = (mesh["shard"].get_local_rank(), mesh["replicate"].get_local_rank())
+    by_coord = dmuon.get_owned_params(model, coord)
+    ctx = dmuon.get_comm_ctx(model)
+    ctx.record_forward_unshard_counter("g", prefetch_hits=2)
+    prof_keep = ctx.consume_forward_unshard_profile(clear=False)
+    prof = dmuon.collect_forward_unshard_profile(model, clear=True, synchronize=False)
+    dmuon.prepare_muon_grads(model, use_reduce_stream=False, coalesce_wait=False)
+    import json
+
+    json.dumps(pg), json.dumps(plan)                                       # JSON-friendly
+    return pg, plan, [p.fqn for p in owned_here], [p.fqn for p in by_coord], prof_keep, prof, \
+        len(list(dmuon.utils.iter_dedicated_states(model)))
+
+
+def test_diagnostics_carry_the_reference_schema_and_signatures():
+    """Code written against the reference's diagnostics keeps working: call
+    forms, top-level keys, per-group and per-parameter keys, totals."""
+    res = run_ranks(_diag_body, 4)
+    pg, plan, owned_here, by_coord, prof_keep, prof, n_states = res[0]
+    assert pg["available"] and pg["num_groups"] == 2 and pg["dedicated_param_count"] == 28
+    assert len(pg["parameters"]) == 5 and pg["parameters_truncated"] == 23
+    assert sum(r[0]["owned_dedicated_param_count"] for r in res) == 28      # every matrix has exactly one owner
+    for key in ("group_index", "group_name", "semantic_group_name", "subgroup_type", "use_muon", "optimizer_param_count",
+                "dedicated_param_count", "owned_dedicated_param_count", "dedicated_muon_param_count",
+                "dedicated_adamw_param_count", "adamw_param_count", "route_param_counts"):
+        assert key in pg["groups"][0], key
+    for key in ("name", "param_name", "route", "param_dtype", "grad_dtype", "output_dtype", "master_dtype", "optim_dtype",
+                "cast_forward_inputs", "matched_policy_overrides", "group_index", "group_name", "owner_rank", "is_owner",
+                "is_dtensor", "uses_sharded_adamw", "numel", "shape"):
+        assert key in pg["parameters"][0], key
+    assert plan["available"] and plan["group_count"] == n_states == 4 and len(plan["groups"]) == 2 and plan["groups_truncated"] == 2
+    g0 = plan["groups"][0]
+    for key in ("group_index", "debug_name", "shard_rank", "replicate_rank", "param_count", "owner_bucket_count",
+                "owner_bucket_bytes", "owner_bucket_bytes_in_order", "owner_buckets", "param_collectives",
+                "param_collectives_truncated"):
+        assert key in g0, key
+    assert len(g0["param_collectives"]) == 3 and g0["param_collectives_truncated"] == g0["param_count"] - 3
+    for key in ("param_index", "param_name", "owner_coord", "bytes", "route", "stage1_shard_reduce_root_global_rank",
+                "stage2_replicate_axis_active_on_this_rank", "stage2_replicate_reduce_root_global_rank",
+                "post_step_replicate_broadcast_root_global_rank"):
+        assert key in g0["param_collectives"][0], key
+    assert sum(g0["owner_bucket_bytes"]) == sum(b["bytes"] for b in g0["owner_buckets"])
+    t = plan["totals"]
+    for key in ("dedicated_local_bytes", "stage1_shard_reduce_tensor_bytes", "stage1_shard_reduce_ring_bytes_per_rank",
+                "stage2_replicate_reduce_tensor_bytes_this_rank", "post_step_replicate_broadcast_tensor_bytes_this_rank",
+                "owner_update_ring_bytes_per_rank", "same_payload_allreduce_ring_bytes_per_rank", "max_owner_bucket_bytes"):
+        assert key in t, key
+    # 28 fp32 matrices of the tiny decoder: 4 layers x (4 x 256x256 + 3 x 256x1024) x 4 bytes
+    assert t["dedicated_local_bytes"] == 4 * (4 * 256 * 256 + 3 * 256 * 1024) * 4
+    assert t["stage1_shard_reduce_ring_bytes_per_rank"] == t["dedicated_local_bytes"]      # 2 * (2 - 1) / 2
+    # the replicate axis is active for the matrices whose owner column this rank sits in: both columns together cover all
+    assert res[0][1]["totals"]["stage2_replicate_reduce_tensor_bytes_this_rank"] + \
+        res[1][1]["totals"]["stage2_replicate_reduce_tensor_bytes_this_rank"] == t["dedicated_local_bytes"]
+    assert owned_here == by_coord
+    assert prof_keep["g"]["prefetch_hits"] == 2 and prof["g"]["prefetch_hits"] == 2

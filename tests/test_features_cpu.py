@@ -127,7 +127,7 @@ def _body_routes_and_groups(rank, world):
         sched.step()
         losses.append(loss.item())
     prof = opt.consume_last_step_profile()
-    summary = dmuon.summarize_param_groups(opt)
+    summary = dmuon.summarize_param_groups(opt)["groups"]
     sd = dmuon.get_model_state_dict(model, rank0_only=False)
     osd = dmuon.get_optimizer_state_dict(model, opt, rank0_only=False)
     bad = None

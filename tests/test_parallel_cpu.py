@@ -68,8 +68,8 @@ def _body_mode(rank, world, mode, reshard, steps):
     losses = _train(rank, world, model, opt, steps)
     sd = dmuon.get_model_state_dict(model, rank0_only=False)
     plan = dmuon.summarize_comm_plan(model)
-    groups = dmuon.summarize_param_groups(opt)
-    return losses, sd, plan["owner_imbalance"], len(groups)
+    groups = dmuon.summarize_param_groups(model, opt)
+    return losses, sd, plan["owner_imbalance"], groups["num_groups"]
 
 
 @pytest.mark.parametrize(

@@ -168,6 +168,28 @@ class DedicatedCommContext:
         for state in self.all_states:
             state.group._post_forward_index = None
 
+    # the reference exposes its five side streams under these names (dmuon/_core/comm.py:98-110); here they are
+    # the streams of the lanes (``None`` on CPU)
+    @property
+    def broadcast_stream(self):
+        return self.broadcast_lane.stream
+
+    @property
+    def sharded_adamw_unshard_stream(self):
+        return self.sharded_adamw_unshard_lane.stream
+
+    @property
+    def reduce_stream(self):
+        return self.reduce_lane.stream
+
+    @property
+    def replicate_reduce_stream(self):
+        return self.replicate_reduce_lane.stream
+
+    @property
+    def replicate_broadcast_stream(self):
+        return self.replicate_broadcast_lane.stream
+
     # ------------------------------------------------------------------ profiling
     def count(self, group_name: str, key: str, inc: int = 1) -> None:
         if self.record_forward_profile or self.record_post_step_profile:

@@ -125,6 +125,12 @@ class DedicatedParamGroup:
         self._tp_gather_ticket: Optional[Ticket] = None
         self._tp_gather_keep: list = []
         self._no_sync = False
+        # HSDP only: with the gate off the shard-axis reduce still runs every backward, but the replicate-axis
+        # reduce waits -- the owner column keeps partial sums -- until a backward with the gate on (the reference's
+        # ``replicate_grads_enabled``, dmuon/_backends/fsdp2/group.py:305-312, FSDP2's "requires all-reduce")
+        self.replicate_grads_enabled = True
+        self._partial_packs: list[_PackedGrad] = []
+        self._partial_flat: dict[int, torch.Tensor] = {}
         self._post_forward_index: Optional[int] = None
         self._backward_done = False
         self._prefetched = False
@@ -167,6 +173,15 @@ class DedicatedParamGroup:
 
     def _global_rank(self, group, local: int) -> int:
         return dist.get_global_rank(group, local) if group is not None and dist.is_initialized() else 0
+
+    @property
+    def reduce_grads_enabled(self) -> bool:
+        """``False`` = the ``no_sync`` state: gradients accumulate locally, nothing travels."""
+        return not self._no_sync
+
+    @reduce_grads_enabled.setter
+    def reduce_grads_enabled(self, value: bool) -> None:
+        self._no_sync = not bool(value)
 
     # ------------------------------------------------------------------ publish
     def unshard(self, prefetch: bool = False) -> None:
@@ -362,11 +377,64 @@ class DedicatedParamGroup:
                     else:
                         out.copy_(padded)
                     self._pending_flat.append((p, out))
+        if self.replicate_size > 1:
+            packs = self._gate_replicate_axis(packs, lane)
         self._stage1_ticket = lane.mark()
         self._pending = packs
         ctx.last_reduced_group = self
         if self.replicate_size > 1 and not self.delay_stage2_to_optimizer:
             self._launch_stage2()
+
+    def _gate_replicate_axis(self, packs: list[_PackedGrad], lane: Lane) -> list[_PackedGrad]:
+        """Gate off: the shard-axis means just queued become (or are added to)
+        partial sums kept on the owner column, and nothing is left for the
+        replicate-axis reduce.  Gate on: partial sums kept earlier join this
+        backward's buffers, so that ONE replicate-axis reduce covers them all."""
+        if self.replicate_grads_enabled and not self._partial_packs and not self._partial_flat:
+            return packs
+        with lane.use(), torch.no_grad():
+            if not self.replicate_grads_enabled:
+                for pack in packs:
+                    if self.shard_rank != pack.coord[0]:
+                        continue            # only the owner's shard column holds a defined shard-axis mean
+                    lane.keep_alive(pack.buf)
+                    ids = [id(p) for p in pack.params]
+                    prev = next((q for q in self._partial_packs
+                                 if q.coord == pack.coord and [id(p) for p in q.params] == ids), None)
+                    if prev is None:
+                        self._partial_packs.append(pack)
+                    else:
+                        prev.buf.add_(pack.buf)
+                for i, (p, out) in enumerate(self._pending_flat):
+                    prev = self._partial_flat.get(id(p))
+                    if prev is None:
+                        self._partial_flat[id(p)] = out
+                    else:
+                        prev.add_(out)
+                self._pending_flat = []
+                return []
+            if self._partial_packs or self._partial_flat:
+                for old in self._partial_packs:
+                    ids = [id(p) for p in old.params]
+                    new = next((q for q in packs if q.coord == old.coord and [id(p) for p in q.params] == ids), None)
+                    if new is None:
+                        packs.append(old)      # another set of parameters than this backward's: reduced on its own
+                    else:
+                        new.buf.add_(old.buf)
+                self._partial_packs = []
+                merged = []
+                for p, out in self._pending_flat:
+                    prev = self._partial_flat.pop(id(p), None)
+                    if prev is not None:
+                        out.add_(prev)
+                    merged.append((p, out))
+                for pid, prev in list(self._partial_flat.items()):
+                    owner = next((q for q in self.flat_params if id(q) == pid), None)
+                    if owner is not None:
+                        merged.append((owner, prev))
+                self._partial_flat = {}
+                self._pending_flat = merged
+        return packs
 
     def _launch_stage2(self) -> None:
         """Replicate-axis mean of what stage 1 left on the owner's shard column."""

@@ -117,6 +117,55 @@ def test_grad_accumulation_with_and_without_no_sync():
         assert (a[n].float() - b[n].float()).abs().max().item() < 1e-4, n
 
 
+def _body_hsdp_gate(rank, world, gate_off_first):
+    """HSDP 2 x 2, two micro-batches per step; optionally the first one runs with
+    the replicate-axis gate off on every group (shard-axis reduce only, partial
+    sums kept on the owner column).  A sharded-AdamW tensor rides along."""
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+    from dmuon_b200.utils import iter_groups
+
+    mesh = init_device_mesh("cpu", (2, world // 2), mesh_dim_names=("replicate", "shard"))
+    model = _build_model()
+    dmuon.dedicate_params(
+        model, mesh["shard"], lambda n, p: _pred(n, p) or n == "norm.weight", replicate_mesh=mesh["replicate"],
+        param_policy={"overrides": [{"name": "norm.weight", "set": {"route": "sharded_adamw"}}]},
+    )
+    for layer in model.layers:
+        fully_shard(layer, mesh=mesh)
+    fully_shard(model, mesh=mesh)
+    opt = dmuon.Muon(model, lr=HP["lr"], adamw_lr=HP["adamw_lr"], weight_decay=HP["weight_decay"],
+                     momentum=HP["momentum"], adamw_weight_decay=HP["adamw_wd"], first_step_progress_log=False)
+    groups = list(iter_groups(model))
+    assert all(g.reduce_grads_enabled and g.replicate_grads_enabled for g in groups)
+    per = 4 // world
+    kept = 0
+    for s in range(2):
+        opt.zero_grad()
+        for micro in range(2):
+            x, y = _data(2 * s + micro)
+            x, y = x[rank * per : (rank + 1) * per], y[rank * per : (rank + 1) * per]
+            for g in groups:
+                g.replicate_grads_enabled = not (gate_off_first and micro == 0)
+            (model(x, labels=y) / 2).backward()
+            if gate_off_first and micro == 0:
+                kept += sum(len(g._partial_packs) + len(g._partial_flat) for g in groups)
+                assert not any(g.has_pending_reduce() for g in groups)       # nothing waits for the replicate axis
+        opt.step()
+        assert not any(g._partial_packs or g._partial_flat for g in groups)
+    return dmuon.get_model_state_dict(model, rank0_only=False), kept
+
+
+def test_hsdp_replicate_axis_gate_defers_stage_two_without_changing_the_result():
+    a = run_ranks(_body_hsdp_gate, 4, args=(False,))
+    b = run_ranks(_body_hsdp_gate, 4, args=(True,))
+    assert a[0][1] == 0 and sum(r[1] for r in b) > 0          # partial sums were really kept somewhere
+    for n in a[0][0]:
+        assert (a[0][0][n].float() - b[0][0][n].float()).abs().max().item() < 1e-5, n
+
+
 def _body_ckpt(rank, world, mode):
     dmuon, model, opt = _setup(rank, world, mode)
     _train(rank, world, model, opt, 2)

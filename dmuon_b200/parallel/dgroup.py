@@ -738,6 +738,24 @@ class DedicatedParamGroup:
     def has_pending_post_step(self) -> bool:
         return self._post_step_ticket is not None or getattr(self, "_tp_ticket", None) is not None
 
+    # Names the reference's groups carry for the same waits and dispatches (dmuon/_backends/fsdp2/group.py,
+    # dmuon/_backends/ddp/group.py); kept so that code that drives a group by hand keeps working.
+    def wait_for_replicate_broadcast(self) -> None:
+        self._pre_forward_wait()
+
+    wait_for_post_step_broadcast = wait_for_replicate_broadcast
+    wait_for_sharded_muon_publish = wait_for_replicate_broadcast
+
+    def wait_for_tp_gather(self) -> None:
+        self.materialize_tp_grads()
+
+    def tp_scatter_delta_async(self, lane: Optional[Lane] = None) -> Optional[Ticket]:
+        return self.tp_scatter_delta(lane)
+
+    def sharded_muon_publish_sync(self) -> None:
+        self.sharded_muon_publish_async()
+        self._pre_forward_wait()
+
     # ------------------------------------------------------------------ ordering helpers
     def _record_post_forward(self) -> None:
         order = self.comm_ctx.post_forward_order

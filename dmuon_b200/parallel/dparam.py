@@ -266,6 +266,13 @@ class DedicatedParam:
                 raise RuntimeError(f"{self.fqn}: gradient shape {tuple(g.shape)} does not match {tuple(self._orig_size)}")
         return g
 
+    def uses_sharded_adamw(self) -> bool:
+        return self._dmuon_route == "sharded_adamw"
+
+    def clear_reduced_grad(self) -> None:
+        self._reduced_grad = None
+        self._sharded_adamw_grad = None
+
     def clear_local_grad(self) -> None:
         if self._unsharded_param is not None:
             self._unsharded_param.grad = None

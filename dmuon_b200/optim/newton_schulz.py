@@ -319,6 +319,14 @@ class NewtonSchulz:
         if backend not in ("gram", "direct"):
             raise ValueError(f"backend must be 'gram' or 'direct', got '{backend}'")
         k = str(kernel).strip().lower()
+        if k == "auto":
+            # as in the reference: the environment variable is consulted only when the argument says "auto"
+            env = __import__("os").environ.get("DMUON_NS_KERNEL", "").strip().lower()
+            if env:
+                if env not in _KERNEL_NAMES + _LEGACY_KERNELS:
+                    raise ValueError(
+                        f"DMUON_NS_KERNEL={env!r} is not valid; choose one of: {', '.join(_KERNEL_NAMES + _LEGACY_KERNELS)}")
+                k = env
         if k in _LEGACY_KERNELS:
             log.info("NewtonSchulz: kernel=%r names a backend of the reference; using the sm_100a kernels", kernel)
             if k == "cublas":

@@ -35,7 +35,10 @@ def _load_builder():
 
 
 def build_kernels() -> None:
-    if os.environ.get("DMUON_BUILD_KERNELS", "1").strip().lower() in ("0", "false", "no", "off"):
+    off = ("0", "false", "no", "off")
+    # DMUON_BUILD_FAST_CLIP is the reference's switch for its only compiled extension; honoured as an alias
+    if (os.environ.get("DMUON_BUILD_KERNELS", "1").strip().lower() in off
+            or os.environ.get("DMUON_BUILD_FAST_CLIP", "1").strip().lower() in off):
         print("dmuon_b200: DMUON_BUILD_KERNELS=0, not compiling the sm_100a kernel library")
         return
     builder = _load_builder()

@@ -310,3 +310,21 @@ def test_newton_schulz_against_svd_polar_factor_and_textbook_iteration(shape, fo
         small = O if shape[0] < shape[1] else O.T
         assert (small @ small.T - torch.eye(small.shape[0])).abs().max().item() < 0.3
     assert (O - newton_schulz_reference(G)).abs().max().item() < 2e-5
+
+
+def test_ns_kernel_environment_variable_applies_only_to_auto(monkeypatch):
+    """``DMUON_NS_KERNEL`` picks the implementation when the argument says
+    "auto" and loses against an explicit argument; the reference's backend
+    names are accepted, unknown names are rejected."""
+    import dmuon_b200 as dmuon
+
+    monkeypatch.delenv("DMUON_NS_KERNEL", raising=False)
+    assert dmuon.NewtonSchulz().kernel == "tcgen05"
+    monkeypatch.setenv("DMUON_NS_KERNEL", "cublas")
+    assert dmuon.NewtonSchulz().kernel == "torch" and dmuon.NewtonSchulz().deterministic
+    assert dmuon.NewtonSchulz(kernel="tcgen05").kernel == "tcgen05"
+    monkeypatch.setenv("DMUON_NS_KERNEL", "quack")
+    assert dmuon.NewtonSchulz().kernel == "tcgen05"
+    monkeypatch.setenv("DMUON_NS_KERNEL", "nonsense")
+    with pytest.raises(ValueError):
+        dmuon.NewtonSchulz()

@@ -168,3 +168,43 @@ def test_group_pipeline_is_bit_identical_to_the_unpipelined_step(mode):
     for r in range(4):
         for n, t in piped[r][0].items():
             assert torch.equal(t, plain[r][0][n]), (mode, r, n)
+
+
+def _double_dispatch_body(rank, world):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+    from test_e2e_cpu import _build_model, _data, _pred
+
+    mesh = init_device_mesh("cpu", (2, world // 2), mesh_dim_names=("replicate", "shard"))
+    model = _build_model()
+    dmuon.dedicate_params(model, mesh["shard"], _pred, replicate_mesh=mesh["replicate"])
+    for layer in model.layers:
+        fully_shard(layer, mesh=mesh)
+    fully_shard(model, mesh=mesh)
+    opt = dmuon.Muon(model, replicate_async=True, first_step_progress_log=False)
+    per = 4 // world
+    x, y = _data(0)
+    model(x[rank * per : (rank + 1) * per], labels=y[rank * per : (rank + 1) * per]).backward()
+    opt.step()
+    pending = any(g.has_pending_post_step() for g in dmuon.utils.iter_groups(model))
+    # a second dispatch while the first has not been consumed by a forward must be refused ...
+    err = None
+    try:
+        dmuon.broadcast_all_updates_async(model)
+    except RuntimeError as exc:
+        err = str(exc)
+    # ... and draining makes the state legal again
+    dmuon.wait_all_replicate_broadcasts(model)
+    drained = not any(g.has_pending_post_step() for g in dmuon.utils.iter_groups(model))
+    dmuon.broadcast_all_updates(model)
+    return pending, err, drained
+
+
+def test_second_async_publish_before_a_forward_is_refused_and_draining_recovers():
+    """One pending publish per group: dispatching again before a forward (or a
+    drain) consumed it raises; ``wait_all_replicate_broadcasts`` is the drain."""
+    for pending, err, drained in run_ranks(_double_dispatch_body, 4):
+        assert pending and drained
+        assert err is not None and "already in flight" in err

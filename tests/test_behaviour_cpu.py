@@ -339,3 +339,39 @@ def test_deferred_gradient_scale_equals_scaling_the_loss():
     # and it is not a no-op: AdamW-routed weights differ from the unscaled run
     diff = max((b[0][0][k].float() - c[0][0][k].float()).abs().max().item() for k in c[0][0] if "proj" not in k)
     assert diff > 1e-6
+
+
+def _ctor_guard_body(rank, world):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+    from test_e2e_cpu import _build_model, _pred
+
+    mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("dp",))
+    errors = []
+    # (1) a model nobody prepared
+    try:
+        dmuon.Muon(_build_model())
+    except RuntimeError as exc:
+        errors.append(str(exc))
+    # (2) dedicated matrices, but the remaining parameters neither sharded nor replicated: they would drift apart
+    model = _build_model()
+    dmuon.dedicate_params(model, mesh, _pred)
+    try:
+        dmuon.Muon(model)
+    except RuntimeError as exc:
+        errors.append(str(exc))
+    # (3) the same model once FSDP2 covers the rest
+    for layer in model.layers:
+        fully_shard(layer, mesh=mesh)
+    fully_shard(model, mesh=mesh)
+    dmuon.Muon(model, first_step_progress_log=False)
+    return errors
+
+
+def test_optimizer_refuses_unprepared_models_and_unmanaged_parameters():
+    for errors in run_ranks(_ctor_guard_body, 2):
+        assert len(errors) == 2
+        assert "dedicate_params" in errors[0]
+        assert "neither dedicated nor covered" in errors[1] and "embed_tokens.weight" in errors[1]

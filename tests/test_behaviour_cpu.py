@@ -375,3 +375,79 @@ def test_optimizer_refuses_unprepared_models_and_unmanaged_parameters():
         assert len(errors) == 2
         assert "dedicate_params" in errors[0]
         assert "neither dedicated nor covered" in errors[1] and "embed_tokens.weight" in errors[1]
+
+
+class _SometimesBlock(nn.Module):
+    def __init__(self, d):
+        super().__init__()
+        self.a_proj = nn.Linear(d, d, bias=False)
+        self.b_proj = nn.Linear(d, d, bias=False)
+        self.b_norm = nn.LayerNorm(d)
+
+    def forward(self, x, use_b):
+        x = x + torch.tanh(self.a_proj(x))
+        if use_b:
+            x = x + torch.tanh(self.b_proj(self.b_norm(x)))
+        return x
+
+
+class _SometimesNet(nn.Module):
+    def __init__(self, vocab=64, d=32):
+        super().__init__()
+        self.embed = nn.Embedding(vocab, d)
+        self.layers = nn.ModuleList(_SometimesBlock(d) for _ in range(2))
+        self.head = nn.Linear(d, vocab, bias=False)
+
+    def forward(self, ids, use_b):
+        x = self.embed(ids)
+        for layer in self.layers:
+            x = layer(x, use_b)
+        return F.cross_entropy(self.head(x).flatten(0, 1), ids.flatten())
+
+
+def _sometimes_data(step):
+    return torch.randint(0, 64, (4, 16), generator=torch.Generator().manual_seed(500 + step))
+
+
+def _sometimes_body(rank, world, steps):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+
+    mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("dp",))
+    torch.manual_seed(3)
+    model = _SometimesNet()
+    dmuon.dedicate_params(model, mesh, lambda n, p: "proj" in n and p.ndim == 2, reshard_after_forward=False)
+    for layer in model.layers:
+        fully_shard(layer, mesh=mesh)
+    fully_shard(model, mesh=mesh)
+    opt = dmuon.Muon(model, lr=0.02, momentum=0.95, weight_decay=0.1, adamw_lr=1e-2, adamw_weight_decay=0.01,
+                     first_step_progress_log=False)
+    per = 4 // world
+    for s in range(steps):
+        ids = _sometimes_data(s)[rank * per : (rank + 1) * per]
+        opt.zero_grad()
+        model(ids, use_b=(s % 2 == 1)).backward()
+        opt.step()
+    return dmuon.get_model_state_dict(model, rank0_only=False)
+
+
+def test_parameters_without_a_gradient_are_skipped_and_keep_their_own_step_count():
+    """A branch that only runs every other step: its Muon matrices and its AdamW
+    tensors are skipped in the steps where they got no gradient (momentum and
+    bias correction advance only when they are used), exactly like the
+    single-process oracle does it."""
+    from oracle import muon_adamw_run
+
+    steps = 5
+    torch.manual_seed(3)
+    ref = _SometimesNet()
+    muon_adamw_run(
+        ref, lambda n, p: "proj" in n and p.ndim == 2, list(range(steps)),
+        lambda m, s: m(_sometimes_data(s), use_b=(s % 2 == 1)),
+        lr=0.02, momentum=0.95, weight_decay=0.1, adamw_lr=1e-2, adamw_wd=0.01, betas=(0.9, 0.999), eps=1e-8,
+    )
+    sd = run_ranks(_sometimes_body, 2, args=(steps,))[0]
+    for n, p in ref.named_parameters():
+        assert (sd[n].float() - p.detach()).abs().max().item() < 5e-4, n

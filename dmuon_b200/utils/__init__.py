@@ -15,7 +15,7 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
-from ..parallel.topology import isolated_process_groups
+from ..parallel.topology import is_isolated_process_group, isolated_process_groups, normalize_owner_rank  # noqa: F401
 
 
 def get_comm_ctx(model: nn.Module):
@@ -53,8 +53,6 @@ def get_owned_params(model: nn.Module, rank=None) -> list:
     ``get_owned_params(model, rank)``) -- by that owner coordinate."""
     if rank is None:
         return [p for p in get_dedicated_params(model) if p.is_owner]
-    from ..parallel.topology import normalize_owner_rank
-
     want = tuple(normalize_owner_rank(rank))
     return [p for p in get_dedicated_params(model) if tuple(p.owner_rank) == want]
 

@@ -104,7 +104,7 @@ def summarize_param_groups(model, optimizer=None, *, max_rows: int = 128) -> dic
         rows.append(
             {
                 "name": dp.fqn,
-                "param_name": dp.fqn,
+                "param_name": str(getattr(dp, "param_name", dp.fqn)),
                 "route": str(dp._dmuon_route),
                 "param_dtype": _dtype(dp._param_dtype),
                 "grad_dtype": _dtype(dp._grad_dtype),
@@ -117,7 +117,7 @@ def summarize_param_groups(model, optimizer=None, *, max_rows: int = 128) -> dic
                 "group_name": groups[gi]["group_name"] if gi is not None else None,
                 "owner_rank": _owner_list(dp.owner_rank),
                 "is_owner": bool(dp.is_owner),
-                "is_dtensor": dp.tp_group is not None,
+                "is_dtensor": bool(getattr(dp, "is_dtensor", False)),
                 "uses_sharded_adamw": dp._dmuon_route == "sharded_adamw",
                 "numel": int(dp.numel),
                 "shape": [int(x) for x in dp.full_shape],

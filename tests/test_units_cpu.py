@@ -328,3 +328,15 @@ def test_ns_kernel_environment_variable_applies_only_to_auto(monkeypatch):
     monkeypatch.setenv("DMUON_NS_KERNEL", "nonsense")
     with pytest.raises(ValueError):
         dmuon.NewtonSchulz()
+
+
+def test_old_partition_import_path_forwards_to_the_real_module():
+    import dmuon_b200.partition as shim
+    from dmuon_b200.parallel import partition as real
+    from dmuon_b200.partition import SMALL_PARAM_THRESHOLD, AssignmentResult, compute_balanced_assignment
+
+    assert compute_balanced_assignment is real.compute_balanced_assignment
+    assert AssignmentResult is real.AssignmentResult and SMALL_PARAM_THRESHOLD == real.SMALL_PARAM_THRESHOLD
+    assert "optimizer_cost_units" in dir(shim) and shim.optimizer_cost_units is real.optimizer_cost_units
+    with pytest.raises(AttributeError):
+        shim.no_such_name

@@ -297,3 +297,47 @@ def test_forward_profile_counters_are_collected_and_drained():
         total_dispatch = sum(v.get("demand_dispatch_calls", 0) + v.get("prefetch_dispatch_calls", 0) for v in prof.values())
         assert total_dispatch >= 2 * 2 * len(prof) - 2
         assert all(not v for v in again.values()) and isinstance(post, dict)
+
+
+def _first_step_log_body(rank, world, enabled, limit):
+    import contextlib
+    import io
+
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+    from test_e2e_cpu import _build_model, _data, _pred
+
+    mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("dp",))
+    model = _build_model()
+    dmuon.dedicate_params(model, mesh, _pred, reshard_after_forward=False)
+    for layer in model.layers:
+        fully_shard(layer, mesh=mesh)
+    fully_shard(model, mesh=mesh)
+    opt = dmuon.Muon(model, first_step_progress_log=enabled, first_step_progress_log_limit=limit)
+    per = 4 // world
+    outs = []
+    for s in range(2):
+        x, y = _data(s)
+        model(x[rank * per : (rank + 1) * per], labels=y[rank * per : (rank + 1) * per]).backward()
+        buf = io.StringIO()
+        with contextlib.redirect_stdout(buf):
+            opt.step()
+        opt.zero_grad()
+        outs.append(buf.getvalue())
+    return outs
+
+
+def test_first_step_progress_lines_are_rank_tagged_limited_and_only_on_the_first_step():
+    on = run_ranks(_first_step_log_body, 2, args=(True, 2))
+    for rank, (first, second) in enumerate(on):
+        lines = [ln for ln in first.splitlines() if ln.startswith("[dmuon_b200]")]
+        assert lines and all(f"[rank={rank}/2]" in ln for ln in lines)
+        assert "first optimizer step started" in lines[0] and "owned_muon_params=" in lines[0]
+        shape_lines = [ln for ln in lines if "Newton-Schulz" in ln and " x " in ln]
+        assert 1 <= len(shape_lines) <= 2                      # first_step_progress_log_limit
+        assert "queued after" in lines[-1]
+        assert second == ""                                    # later steps are silent
+    off = run_ranks(_first_step_log_body, 2, args=(False, 8))
+    assert all(first == "" and second == "" for first, second in off)

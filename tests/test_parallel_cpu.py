@@ -220,3 +220,53 @@ def test_loading_a_plain_single_process_state_dict(mode):
         for k in plain:
             assert torch.equal(back[k], plain[k]), k
         assert abs(loss - want) < 1e-5 * max(1.0, abs(want))
+
+
+def _body_invariants(rank, world):
+    import torch.distributed as dist
+
+    dmuon, model, opt = _setup(rank, world, "hsdp")
+    dps = dmuon.get_dedicated_params(model)
+    facts = {
+        p.fqn: (tuple(p.owner_rank), bool(p.is_owner), bool(p.in_owner_column), p._owned_data is not None,
+                (p.shard_rank, p.replicate_rank))
+        for p in dps
+    }
+    # one backward without a step: who ends up holding a reduced gradient?
+    x, y = _data(0)
+    per = 4 // world
+    model(x[rank * per : (rank + 1) * per], labels=y[rank * per : (rank + 1) * per]).backward()
+    dmuon.prepare_muon_grads(model)
+    has_grad = {p.fqn: p._reduced_grad is not None for p in dps}
+    opt.step()
+    dmuon.wait_all_replicate_broadcasts(model)
+    # after the publish every rank of the owner's shard column holds the same master
+    digests = {}
+    for p in dps:
+        if p._owned_data is not None:
+            digests[p.fqn] = float(p._owned_data.double().sum())
+    gathered = [None] * world
+    dist.all_gather_object(gathered, digests)
+    return facts, has_grad, gathered
+
+
+def test_ownership_invariants_on_a_replicate_by_shard_grid():
+    """One global owner per matrix; master weights exactly on the owner's shard
+    column (all replicate indices of the owner's shard index); only the owner ends
+    up with a reduced gradient; after the post-step publish the column's copies
+    agree."""
+    res = run_ranks(_body_invariants, 4)
+    names = list(res[0][0])
+    for n in names:
+        owners = [r for r in range(4) if res[r][0][n][1]]
+        assert len(owners) == 1, (n, owners)                                   # I1
+        coord = res[0][0][n][0]
+        for r in range(4):
+            _, is_owner, in_col, has_master, (srank, rrank) = res[r][0][n]
+            assert in_col == (srank == coord[0])
+            assert has_master == in_col, (n, r)                                # I2
+            assert is_owner == (in_col and rrank == coord[1])
+            assert res[r][1][n] == is_owner, (n, r)                            # I3
+        column = [r for r in range(4) if res[r][0][n][2]]
+        vals = [res[0][2][r][n] for r in column]
+        assert len(column) == 2 and abs(vals[0] - vals[1]) < 1e-9, (n, vals)   # I4

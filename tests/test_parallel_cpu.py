@@ -270,3 +270,59 @@ def test_ownership_invariants_on_a_replicate_by_shard_grid():
         column = [r for r in range(4) if res[r][0][n][2]]
         vals = [res[0][2][r][n] for r in column]
         assert len(column) == 2 and abs(vals[0] - vals[1]) < 1e-9, (n, vals)   # I4
+
+
+def _body_state_dtype(rank, world):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+
+    mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("dp",))
+
+    def build(optim_dtype):
+        model = _build_model()
+        dmuon.dedicate_params(model, mesh, lambda n, p: _pred(n, p) or n == "norm.weight", reshard_after_forward=False,
+                              param_policy={"defaults": {"optim_dtype": optim_dtype}})
+        for layer in model.layers:
+            fully_shard(layer, mesh=mesh)
+        fully_shard(model, mesh=mesh)
+        return model, dmuon.Muon(model, first_step_progress_log=False)
+
+    # train with fp32 optimizer state, save ...
+    model, opt = build("fp32")
+    per = 4 // world
+    x, y = _data(0)
+    model(x[rank * per : (rank + 1) * per], labels=y[rank * per : (rank + 1) * per]).backward()
+    opt.step()
+    msd = dmuon.get_model_state_dict(model, rank0_only=False)
+    osd = dmuon.get_optimizer_state_dict(model, opt, rank0_only=False)
+    saved = {k: v["momentum_buffer"].dtype for k, v in osd["dedicated"].items()}
+    # ... and restore into a set-up whose policy keeps optimizer state in bf16
+    model2, opt2 = build("bf16")
+    dmuon.set_model_state_dict(model2, msd)
+    dmuon.set_optimizer_state_dict(model2, opt2, osd)
+    got = {}
+    for dp in dmuon.get_owned_params(model2):
+        st = opt2.state[id(dp)]
+        for key in ("momentum_buffer", "exp_avg", "exp_avg_sq"):
+            if key in st:
+                ref = osd["dedicated" if key == "momentum_buffer" else "dedicated_adamw"][dp.fqn][key]
+                got[(dp.fqn, key)] = (st[key].dtype, float((st[key].float() - ref.float().reshape(st[key].shape)).abs().max()),
+                                      float(ref.float().abs().max()))
+    return saved, got
+
+
+def test_restored_optimizer_state_takes_the_policy_dtype():
+    """Momentum and dedicated-AdamW moments saved in fp32 load into a set-up whose
+    ``optim_dtype`` is bf16 as bf16 tensors with the same values (to bf16
+    rounding), as the reference does for the momentum
+    (tests/unit/test_checkpoint_state_dtype.py:13-39)."""
+    seen = 0
+    for saved, got in run_ranks(_body_state_dtype, 2):
+        assert saved and all(d == torch.float32 for d in saved.values())
+        for (name, key), (dtype, err, scale) in got.items():
+            assert dtype == torch.bfloat16, (name, key, dtype)
+            assert err <= 8e-3 * max(scale, 1e-12), (name, key, err, scale)
+            seen += 1
+    assert seen >= 28        # every Muon matrix on its owner, plus the AdamW-routed norm weight's two moments

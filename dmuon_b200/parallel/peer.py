@@ -96,6 +96,20 @@ def peer_backend_requested() -> str:
     return os.environ.get("DMUON_COMM_BACKEND", "auto").strip().lower()
 
 
+def spans_hosts() -> bool:
+    """True when the launcher says the job runs on more than one host
+    (``LOCAL_WORLD_SIZE``, set by ``torchrun``, smaller than the world size).
+    Peer memory needs every rank of a group on one NVLink domain; without the
+    variable (single-host spawners) nothing is assumed."""
+    local = os.environ.get("LOCAL_WORLD_SIZE")
+    if not local or not (dist.is_available() and dist.is_initialized()):
+        return False
+    try:
+        return dist.get_world_size() > int(local)
+    except ValueError:
+        return False
+
+
 def peer_backend_possible(device: torch.device, dp_group, replicate_group, dparams) -> Optional[str]:
     """None when usable, else the reason it is not."""
     if device.type != "cuda":
@@ -104,6 +118,8 @@ def peer_backend_possible(device: torch.device, dp_group, replicate_group, dpara
         return "single rank"
     if dp_group.size() > MAX_PEERS:
         return f"more than {MAX_PEERS} ranks on the shard axis"
+    if spans_hosts():
+        return "the job spans more than one host"
     if replicate_group is not None and replicate_group.size() > 1:
         return "replicate axis present"
     if any(p.tp_group is not None for p in dparams):
@@ -130,6 +146,8 @@ def peer_backend_possible_from_policies(device, dp_group, replicate_group, param
         return "single rank"
     if dp_group.size() > MAX_PEERS:
         return f"more than {MAX_PEERS} ranks on the shard axis"
+    if spans_hosts():
+        return "the job spans more than one host"
     if replicate_group is not None and replicate_group.size() > 1:
         return "replicate axis present"
     if any(is_tp(p) for p in params):

@@ -55,7 +55,9 @@ def tp_peer_possible(device: torch.device, tp_group) -> Optional[str]:
         return "single rank"
     if tp_group.size() > MAX_PEERS:
         return f"more than {MAX_PEERS} tensor-parallel ranks"
-    if dist.get_world_size() > torch.cuda.device_count():
+    from .peer import spans_hosts
+
+    if dist.get_world_size() > torch.cuda.device_count() or spans_hosts():
         return "the job spans more than one host"
     try:
         import torch.distributed._symmetric_memory as _symm  # noqa: F401  (an alias: a plain "import torch.x" would

@@ -341,3 +341,28 @@ def test_first_step_progress_lines_are_rank_tagged_limited_and_only_on_the_first
         assert second == ""                                    # later steps are silent
     off = run_ranks(_first_step_log_body, 2, args=(False, 8))
     assert all(first == "" and second == "" for first, second in off)
+
+
+def _spans_hosts_body(rank, world):
+    import os
+
+    from dmuon_b200.parallel.peer import spans_hosts
+
+    out = []
+    for val in (None, str(world), "1", "not-a-number"):
+        if val is None:
+            os.environ.pop("LOCAL_WORLD_SIZE", None)
+        else:
+            os.environ["LOCAL_WORLD_SIZE"] = val
+        out.append(spans_hosts())
+    return out
+
+
+def test_peer_plane_stays_off_when_the_launcher_reports_several_hosts():
+    """``LOCAL_WORLD_SIZE`` smaller than the world size means ranks on other
+    hosts: peer memory is then not considered (no variable: nothing is assumed)."""
+    from dmuon_b200.parallel.peer import spans_hosts
+
+    assert spans_hosts() is False                      # no process group here
+    for got in run_ranks(_spans_hosts_body, 2):
+        assert got == [False, False, True, False]

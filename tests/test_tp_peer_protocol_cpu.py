@@ -1,0 +1,172 @@
+"""Pure-Python model of the tensor-parallel peer exchange's flag protocol
+(``parallel/tp_peer.py``), explored over random interleavings of every rank's
+three streams.
+
+Per optimizer step the layers are worked through in blocks.  For block ``b`` a rank
+
+    gather lane    (first gather of the step) wait GRAD_CONSUMED[all] >= gathers completed before this step;
+                   write its shard slots of block b; signal GRAD_READY[self] = number of gathers so far
+    compute        wait GRAD_READY[all] >= number of gathers ISSUED so far (the next block's gather is issued
+                   before this block computes); read every rank's shard slots of block b;
+                   (first block of the step) wait DELTA_CONSUMED[all] >= scatters completed before this step;
+                   write its update slots of block b
+    scatter lane   signal DELTA_READY[self] = scatters so far; wait DELTA_READY[all] >= that; read the owners'
+                   update slots of block b; signal DELTA_CONSUMED[self] = the same number
+    compute        (end of step) signal GRAD_CONSUMED[self] = gathers so far
+
+A lane "follows" another stream at the moment its work is issued: it may not
+start before everything issued earlier on that stream has finished.  Flags only
+grow.  The model checks that no interleaving the waits allow lets a rank read a
+slot of the wrong step or overwrite one that is still to be read, that nothing
+deadlocks -- and that leaving out any one wait, or waiting for "consumed" before
+EVERY gather instead of before the first one of a step (a fault this exchange once
+had: the flag is only raised at the end of a step), is caught.
+"""
+import random
+
+import pytest
+
+GRAD_READY, GRAD_CONSUMED, DELTA_READY, DELTA_CONSUMED = range(4)
+COMPUTE, GATHER, SCATTER = range(3)
+
+
+class Violation(AssertionError):
+    pass
+
+
+class Deadlock(AssertionError):
+    pass
+
+
+def _program(world, steps, blocks, drop=None, consumed_wait_every_gather=False):
+    """Per-stream op lists of one rank with cross-stream dependencies.  Every rank
+    runs the same program (the flag indices it signals are its own)."""
+    streams = {COMPUTE: [], GATHER: [], SCATTER: []}
+    issued = {COMPUTE: 0, GATHER: 0, SCATTER: 0}          # ops issued so far per stream
+
+    def emit(stream, op, follow=()):
+        # an op may start once the ops issued before it on its own stream are done (implicit) and the first
+        # ``n`` ops of every followed stream are done
+        deps = {f: issued[f] for f in follow}
+        streams[stream].append((op, deps))
+        issued[stream] += 1
+
+    gathers = scatters = 0
+    for s in range(steps):
+        gathers_at_start, scatters_at_start = gathers, scatters
+
+        def prepare(b, first):
+            nonlocal gathers
+            if (first or consumed_wait_every_gather) and drop != "grad_consumed":
+                want = gathers if consumed_wait_every_gather else gathers_at_start
+                emit(GATHER, ("wait", GRAD_CONSUMED, want), follow=(COMPUTE,))
+            emit(GATHER, ("write_shard", b, s), follow=(COMPUTE,))
+            gathers += 1
+            emit(GATHER, ("signal", GRAD_READY, gathers))
+
+        prepare(0, True)
+        for b in range(blocks):
+            if b + 1 < blocks:
+                prepare(b + 1, False)
+            if drop != "grad_ready":
+                emit(COMPUTE, ("wait", GRAD_READY, gathers))
+            emit(COMPUTE, ("read_shards", b, s))
+            if b == 0 and drop != "delta_consumed":
+                emit(COMPUTE, ("wait", DELTA_CONSUMED, scatters_at_start))
+            emit(COMPUTE, ("write_delta", b, s))
+            scatters += 1
+            emit(SCATTER, ("signal", DELTA_READY, scatters), follow=(COMPUTE, GATHER))
+            if drop != "delta_ready":
+                emit(SCATTER, ("wait", DELTA_READY, scatters))
+            emit(SCATTER, ("read_deltas", b, s))
+            emit(SCATTER, ("signal", DELTA_CONSUMED, scatters))
+        emit(COMPUTE, ("signal", GRAD_CONSUMED, gathers))
+    return streams
+
+
+def simulate(world, steps, blocks, seed, **variant):
+    rng = random.Random(seed)
+    progs = [_program(world, steps, blocks, **variant) for _ in range(world)]
+    done = [{st: 0 for st in (COMPUTE, GATHER, SCATTER)} for _ in range(world)]
+    flags = [[0] * world for _ in range(4)]
+    shard = [[-1] * blocks for _ in range(world)]          # step whose gradient a rank's slot of block b holds
+    delta = [[-1] * blocks for _ in range(world)]          # step whose update an owner's slot of block b holds
+    shard_reads = [[0] * blocks for _ in range(world)]     # how many ranks have read slot (rank, b) of the current step
+    delta_reads = [[0] * blocks for _ in range(world)]
+
+    def runnable(r, st):
+        i = done[r][st]
+        if i >= len(progs[r][st]):
+            return False
+        op, deps = progs[r][st][i]
+        if any(done[r][f] < n for f, n in deps.items()):
+            return False
+        if op[0] == "wait":
+            return all(flags[op[1]][q] >= op[2] for q in range(world))
+        return True
+
+    total = sum(len(p[st]) for p in progs for st in p)
+    for _ in range(total):
+        ready = [(r, st) for r in range(world) for st in (COMPUTE, GATHER, SCATTER) if runnable(r, st)]
+        if not ready:
+            raise Deadlock(f"seed {seed}: no stream can make progress")
+        r, st = rng.choice(ready)
+        op, _ = progs[r][st][done[r][st]]
+        kind = op[0]
+        if kind == "signal":
+            flags[op[1]][r] = max(flags[op[1]][r], op[2])
+        elif kind == "write_shard":
+            b, s = op[1], op[2]
+            if shard[r][b] >= 0 and shard_reads[r][b] < world:
+                raise Violation(f"seed {seed}: rank {r} overwrites its shard of block {b} (step {shard[r][b]}) before every "
+                                "TP owner has read it")
+            shard[r][b], shard_reads[r][b] = s, 0
+        elif kind == "read_shards":
+            b, s = op[1], op[2]
+            for q in range(world):
+                if shard[q][b] != s:
+                    raise Violation(f"seed {seed}: rank {r} reads rank {q}'s shard of block {b} holding step {shard[q][b]}, "
+                                    f"wanted step {s}")
+                shard_reads[q][b] += 1
+        elif kind == "write_delta":
+            b, s = op[1], op[2]
+            if delta[r][b] >= 0 and delta_reads[r][b] < world:
+                raise Violation(f"seed {seed}: rank {r} overwrites its update of block {b} (step {delta[r][b]}) before every "
+                                "rank has applied its slice")
+            delta[r][b], delta_reads[r][b] = s, 0
+        elif kind == "read_deltas":
+            b, s = op[1], op[2]
+            for q in range(world):
+                if delta[q][b] != s:
+                    raise Violation(f"seed {seed}: rank {r} reads rank {q}'s update of block {b} holding step {delta[q][b]}, "
+                                    f"wanted step {s}")
+                delta_reads[q][b] += 1
+        done[r][st] += 1
+
+
+@pytest.mark.parametrize("world,blocks", [(2, 1), (2, 3), (4, 2), (8, 4)])
+def test_exchange_protocol_is_safe_and_live_under_random_interleavings(world, blocks):
+    for seed in range(150):
+        simulate(world, steps=4, blocks=blocks, seed=seed)
+
+
+@pytest.mark.parametrize("drop", ["grad_ready", "grad_consumed", "delta_ready", "delta_consumed"])
+def test_every_wait_of_the_exchange_is_necessary(drop):
+    caught = 0
+    for seed in range(300):
+        try:
+            simulate(3, steps=4, blocks=2, seed=seed, drop=drop)
+        except Violation:
+            caught += 1
+    assert caught > 0, f"leaving out the {drop} wait went unnoticed: the model's checks are vacuous"
+
+
+def test_waiting_for_consumed_before_every_gather_cannot_make_progress():
+    """"Consumed" is raised once, at the end of a step.  A gather after the first
+    one of a step that waits for the count of gathers so far therefore waits for a
+    flag that only the end of this very step raises: on the GPU the bounded wait
+    runs out (status word set), in the model nothing can move."""
+    with pytest.raises(Deadlock):
+        simulate(2, steps=2, blocks=2, seed=0, consumed_wait_every_gather=True)
+    # with one block per step the two readings of the rule coincide
+    simulate(2, steps=3, blocks=1, seed=0, consumed_wait_every_gather=True)

@@ -221,9 +221,12 @@ def test_peer_data_plane_matches_nccl():
         assert abs(a - b) < 2e-2 * max(1.0, abs(b)), (got[0][0], ref[0][0])
         assert abs(c - b) < 2e-2 * max(1.0, abs(b)), (alt[0][0], ref[0][0])
     # Two separate runs never see bit-identical gradients (the attention backward
-    # and the sharded reductions are not deterministic) and Newton-Schulz amplifies
-    # such differences along weak singular directions, so this end-to-end check is a
-    # sanity bound; exactness of reduce and publish is asserted by the test below.
+    # and the sharded reductions are not deterministic) and the fp16 Gram iteration
+    # amplifies last-bit differences along singular directions below fp16's
+    # resolution of the Gram matrix: two runs of ONE implementation already differ
+    # by 1-4 % in square matrices after three steps (measured in
+    # tests/test_tp_peer_gpu.py).  So this end-to-end check is a sanity bound;
+    # exactness of reduce and publish is asserted by the test below.
     for k, v in ref[0][1].items():
         rel = (got[0][1][k].float() - v.float()).norm().item() / (v.float().norm().item() + 1e-12)
         assert rel < 0.15, (k, rel)

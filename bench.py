@@ -579,6 +579,22 @@ def run(args):
     step_ms, opt_ms, e2e_max = (float(x) for x in t.tolist())
     peak = torch.tensor([torch.cuda.max_memory_allocated() / 2**30], device=device)
     dist.all_reduce(peak, op=dist.ReduceOp.MAX)
+    # every device-side wait of this package is bounded and records in a status word when it ran out; a run in which
+    # that happened on any rank did not do the work it claims to have timed
+    status_code = 0
+    try:
+        status = torch.zeros(1, dtype=torch.int32, device=device)
+        if args.impl == "ours":
+            from dmuon_b200.ops import gemm as _gemm
+
+            status.copy_(_gemm.status_buffer(device)[:1])
+        dist.all_reduce(status, op=dist.ReduceOp.MAX)
+        status_code = int(status.item())
+    except Exception as exc:          # the check itself must not cost a measurement
+        print(f"bench.py: could not read the kernel status word ({exc})", file=sys.stderr)
+        status_code = -1
+    if status_code > 0:
+        raise RuntimeError(f"a kernel wait ran out during the benchmark (status code {status_code}): no valid timing")
     tokens = mb * seq * data_ranks
     if rank == 0:
         adamw_ms = adamw_step_ms(args, world) if args.optimizer == "muon" else None
@@ -611,6 +627,7 @@ def run(args):
             "loss": last_loss,
             "peak_mem_gib": round(float(peak.item()), 2),
             "gpu_launches": int(l1 - l0),
+            "kernel_status": status_code,
             "clocks": clocks,
             "config": {
                 "model": args.model,

@@ -453,6 +453,7 @@ class Muon(torch.optim.Optimizer):
             with torch.enable_grad():
                 loss = closure()
         self._step_count += 1
+        self._raise_if_a_kernel_wait_ran_out()
         started = self._first_step_begin()
         try:
             self._step_impl()
@@ -460,7 +461,64 @@ class Muon(torch.optim.Optimizer):
             self._first_step_end(started, failed=True)
             raise
         self._first_step_end(started)
+        self._poll_kernel_status()
         return loss
+
+    # ------------------------------------------------------------------ device status word
+    def _status_watch_enabled(self) -> bool:
+        if self.device.type != "cuda":
+            return False
+        return os.environ.get("DMUON_STATUS_WATCH", "1").strip().lower() not in ("0", "false", "no", "off")
+
+    def _poll_kernel_status(self) -> None:
+        """Queue a 16-byte copy of the device's status word (where kernels record
+        a bounded wait that ran out) into pinned host memory, behind this step.
+        Nothing waits for it: the NEXT step looks at it if the copy has landed."""
+        if getattr(self, "_status_watch_broken", False) or not self._status_watch_enabled() or not _kernels_ok():
+            return
+        from ..ops import gemm as G
+
+        try:
+            if getattr(self, "_status_host", None) is None:
+                self._status_host = torch.zeros(4, dtype=torch.int32).pin_memory()
+                self._status_event = torch.cuda.Event()
+            self._status_host.copy_(G.status_buffer(self.device), non_blocking=True)
+            self._status_event.record(torch.cuda.current_stream(self.device))
+            self._status_polled = True
+        except Exception as exc:      # a watch that cannot be set up (no pinned memory, stream capture) must not stop training
+            self._status_watch_broken = True
+            self._status_polled = False
+            log.warning("dmuon_b200: kernel status watch switched off (%s); call check_kernel_status() by hand", exc)
+
+    def _raise_if_a_kernel_wait_ran_out(self) -> None:
+        """Report, one step late and without synchronising, that a kernel gave up
+        waiting (a peer that never signalled, a stalled pipeline): training on
+        after that would use stale weights or gradients."""
+        if not getattr(self, "_status_polled", False):
+            return
+        try:
+            if not self._status_event.query():
+                return
+            code = int(self._status_host[0])
+        except Exception as exc:
+            self._status_watch_broken, self._status_polled = True, False
+            log.warning("dmuon_b200: kernel status watch switched off (%s); call check_kernel_status() by hand", exc)
+            return
+        self._status_polled = False
+        if code != 0:
+            from ..ops import gemm as G
+
+            G.status_buffer(self.device).zero_()
+            raise G.KernelTimeout(
+                f"dmuon_b200 kernel wait ran out during the previous step (code {code}: {G.describe_status(code)})")
+
+    def check_kernel_status(self) -> None:
+        """Synchronising form of the same check (end of training, before a
+        checkpoint is trusted)."""
+        if self.device.type == "cuda" and _kernels_ok():
+            from ..ops import gemm as G
+
+            G.check_status(self.device)
 
     # ------------------------------------------------------------------ group pipeline
     def _has_post_step_traffic(self, g) -> bool:

@@ -451,3 +451,60 @@ def test_parameters_without_a_gradient_are_skipped_and_keep_their_own_step_count
     sd = run_ranks(_sometimes_body, 2, args=(steps,))[0]
     for n, p in ref.named_parameters():
         assert (sd[n].float() - p.detach()).abs().max().item() < 5e-4, n
+
+
+def _status_watch_body(rank, world):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+    from dmuon_b200.ops import gemm as G
+    from test_e2e_cpu import _build_model, _data, _pred
+
+    mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("dp",))
+    model = _build_model()
+    dmuon.dedicate_params(model, mesh, _pred, reshard_after_forward=False)
+    for layer in model.layers:
+        fully_shard(layer, mesh=mesh)
+    fully_shard(model, mesh=mesh)
+    opt = dmuon.Muon(model, first_step_progress_log=False)
+    x, y = _data(0)
+    model(x, labels=y).backward()
+    opt.step()                                      # on CPU nothing is polled
+    polled_on_cpu = getattr(opt, "_status_polled", False)
+
+    class _Landed:
+        def query(self):
+            return True
+
+    class _InFlight:
+        def query(self):
+            return False
+
+    # what a GPU step leaves behind: a host copy of the status word and the event that says it has landed
+    fake_device_word = torch.tensor([4, 0, 0, 0], dtype=torch.int32)
+    G_status = G.status_buffer
+    G.status_buffer = lambda device: fake_device_word
+    try:
+        opt._status_host, opt._status_event, opt._status_polled = torch.tensor([4, 0, 0, 0], dtype=torch.int32), _InFlight(), True
+        opt._raise_if_a_kernel_wait_ran_out()       # the copy has not landed: nothing is concluded, nothing waits
+        still_pending = opt._status_polled
+        opt._status_event = _Landed()
+        msg = None
+        try:
+            opt._raise_if_a_kernel_wait_ran_out()
+        except G.KernelTimeout as exc:
+            msg = str(exc)
+        cleared = int(fake_device_word[0]) == 0 and not opt._status_polled
+        opt._status_host, opt._status_polled = torch.zeros(4, dtype=torch.int32), True
+        opt._raise_if_a_kernel_wait_ran_out()       # a clean word raises nothing
+    finally:
+        G.status_buffer = G_status
+    return polled_on_cpu, still_pending, msg, cleared
+
+
+def test_a_wait_that_ran_out_is_reported_on_the_next_step_without_synchronising():
+    (polled_on_cpu, still_pending, msg, cleared), = run_ranks(_status_watch_body, 1)
+    assert polled_on_cpu is False and still_pending is True
+    assert msg is not None and "code 4" in msg and "previous step" in msg
+    assert cleared

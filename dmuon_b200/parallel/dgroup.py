@@ -34,6 +34,10 @@ from .comm import DedicatedCommContext, Lane, Ticket
 from .dparam import DedicatedParam, alloc_storage, free_storage
 
 
+#: ``DMUON_CHECK_GRAD_PRESENCE=1``: verify in every backward that all ranks hold gradients for the same parameters
+CHECK_GRAD_PRESENCE = __import__("os").environ.get("DMUON_CHECK_GRAD_PRESENCE", "0").strip().lower() in ("1", "true", "yes", "on")
+
+
 def _has_avg(group) -> bool:
     try:
         return dist.get_backend(group) == "nccl"
@@ -285,10 +289,39 @@ class DedicatedParamGroup:
     def _grad_dtype_of(self, p: DedicatedParam, g: torch.Tensor) -> torch.dtype:
         return p._grad_dtype or g.dtype
 
+    def check_grad_presence(self, have: list[bool]) -> None:
+        """Debugging aid (``DMUON_CHECK_GRAD_PRESENCE=1``): every rank of the
+        data-parallel group must produce gradients for the SAME dedicated
+        parameters of a group in a backward -- the reduce is packed per owner,
+        so a rank without a gradient (an expert that got no token, a branch one
+        rank skipped) would send a buffer of another size or no buffer at all,
+        and the job would hang.  Gathers the presence flags (a host
+        synchronisation) and raises with the names and ranks that differ."""
+        if self.dp_group is None or self.shard_size < 2:
+            return
+        mine = [bool(h) for h in have]
+        everyone: list = [None] * self.shard_size
+        dist.all_gather_object(everyone, mine, group=self.dp_group)
+        if all(e == everyone[0] for e in everyone):
+            return
+        lines = []
+        for i, p in enumerate(self.params):
+            ranks = [r for r, e in enumerate(everyone) if e[i]]
+            if 0 < len(ranks) < self.shard_size:
+                lines.append(f"{p.fqn}: gradient on data-parallel ranks {ranks} only")
+        raise RuntimeError(
+            f"group {self.name}: ranks disagree about which dedicated parameters have a gradient in this backward; "
+            + "; ".join(lines[:8]) + (" ..." if len(lines) > 8 else "")
+            + ".  Make the unused path contribute a zero (e.g. add `0 * module(x[:0]).sum()` to the loss) or exclude "
+            "the parameter from dedicate_params."
+        )
+
     def reduce_grads(self) -> None:
         """Pack this backward's gradients per owner and start the mean-reduce."""
         ctx = self.comm_ctx
         with_grad = [(p, p.local_grad()) for p in self.params]
+        if CHECK_GRAD_PRESENCE and not self._no_sync:
+            self.check_grad_presence([g is not None for _, g in with_grad])
         with_grad = [(p, g) for p, g in with_grad if g is not None]
         if not with_grad:
             return

@@ -50,6 +50,7 @@ import torch
 import torch.distributed as dist
 from torch.profiler import record_function
 
+from . import dgroup as _dgroup
 from .dgroup import DedicatedParamGroup
 from .dparam import DedicatedParam
 
@@ -829,6 +830,9 @@ class PeerParamGroup(DedicatedParamGroup):
         with_grad = [(p, p.local_grad()) for p in self.bcast_params]
         # gradients the backward GEMMs already wrote into the arena
         direct = [p for p, g in with_grad if getattr(p, "_grad_in_arena", False)]
+        if _dgroup.CHECK_GRAD_PRESENCE and not self._no_sync and len(self.bcast_params) == len(self.params):
+            # debugging aid: a rank that produced no gradient for a slot leaves LAST step's data there for the owner to sum
+            self.check_grad_presence([g is not None or getattr(p, "_grad_in_arena", False) for p, g in with_grad])
         with_grad = [(p, g) for p, g in with_grad if g is not None]
         if not with_grad and not direct:
             return

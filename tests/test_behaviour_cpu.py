@@ -508,3 +508,42 @@ def test_a_wait_that_ran_out_is_reported_on_the_next_step_without_synchronising(
     assert polled_on_cpu is False and still_pending is True
     assert msg is not None and "code 4" in msg and "previous step" in msg
     assert cleared
+
+
+def _presence_body(rank, world):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+    from dmuon_b200.parallel import dgroup
+
+    dgroup.CHECK_GRAD_PRESENCE = True          # what DMUON_CHECK_GRAD_PRESENCE=1 sets at import
+    mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("dp",))
+    torch.manual_seed(3)
+    model = _SometimesNet()
+    dmuon.dedicate_params(model, mesh, lambda n, p: "proj" in n and p.ndim == 2, reshard_after_forward=False)
+    for layer in model.layers:
+        fully_shard(layer, mesh=mesh)
+    fully_shard(model, mesh=mesh)
+    opt = dmuon.Muon(model, first_step_progress_log=False)
+    ids = _sometimes_data(0)[rank * 2 : rank * 2 + 2]
+    # same branch on every rank: fine
+    model(ids, use_b=True).backward()
+    opt.step()
+    opt.zero_grad()
+    # rank 0 takes the optional branch, rank 1 does not: b_proj has a gradient on rank 0 only
+    err = None
+    try:
+        model(ids, use_b=(rank == 0)).backward()
+    except RuntimeError as exc:
+        err = str(exc)
+    return err
+
+
+def test_debug_check_names_parameters_whose_gradient_exists_on_some_ranks_only():
+    """The packed reduce needs the same parameters to have gradients on every
+    rank; with ``DMUON_CHECK_GRAD_PRESENCE=1`` a disagreement is reported (instead
+    of a hang) with the parameter and the ranks."""
+    for err in run_ranks(_presence_body, 2):
+        assert err is not None and "ranks disagree" in err
+        assert "b_proj.weight: gradient on data-parallel ranks [0] only" in err

@@ -38,6 +38,22 @@ from .dparam import DedicatedParam, alloc_storage, free_storage
 CHECK_GRAD_PRESENCE = __import__("os").environ.get("DMUON_CHECK_GRAD_PRESENCE", "0").strip().lower() in ("1", "true", "yes", "on")
 
 
+#: ``DMUON_ZERO_FILL_MISSING_GRADS=1``: a dedicated parameter without a gradient in a backward (an expert that got no
+#: token on this rank) contributes zeros, so that every rank sends the same buffers whatever its data did
+ZERO_FILL_MISSING_GRADS = __import__("os").environ.get("DMUON_ZERO_FILL_MISSING_GRADS", "0").strip().lower() in ("1", "true", "yes", "on")
+
+
+def zero_fill_missing(with_grad: list, device) -> list:
+    """``(param, grad or None)`` pairs with every ``None`` replaced by zeros of
+    the parameter's local shape and gradient dtype."""
+    out = []
+    for p, g in with_grad:
+        if g is None:
+            g = torch.zeros(p._orig_size, dtype=p._grad_dtype or p._param_dtype, device=device)
+        out.append((p, g))
+    return out
+
+
 def _has_avg(group) -> bool:
     try:
         return dist.get_backend(group) == "nccl"
@@ -320,6 +336,9 @@ class DedicatedParamGroup:
         """Pack this backward's gradients per owner and start the mean-reduce."""
         ctx = self.comm_ctx
         with_grad = [(p, p.local_grad()) for p in self.params]
+        if ZERO_FILL_MISSING_GRADS and not self._no_sync:
+            # rank-independent participation: whatever has no gradient here sends zeros (see the switch above)
+            with_grad = zero_fill_missing(with_grad, self.device)
         if CHECK_GRAD_PRESENCE and not self._no_sync:
             self.check_grad_presence([g is not None for _, g in with_grad])
         with_grad = [(p, g) for p, g in with_grad if g is not None]

@@ -830,6 +830,10 @@ class PeerParamGroup(DedicatedParamGroup):
         with_grad = [(p, p.local_grad()) for p in self.bcast_params]
         # gradients the backward GEMMs already wrote into the arena
         direct = [p for p, g in with_grad if getattr(p, "_grad_in_arena", False)]
+        if _dgroup.ZERO_FILL_MISSING_GRADS and not self._no_sync:
+            # a slot nobody wrote would still hold last step's gradient when the owner sums the arenas
+            with_grad = [(p, g) if (g is not None or getattr(p, "_grad_in_arena", False)) else
+                         _dgroup.zero_fill_missing([(p, None)], self.device)[0] for p, g in with_grad]
         if _dgroup.CHECK_GRAD_PRESENCE and not self._no_sync and len(self.bcast_params) == len(self.params):
             # debugging aid: a rank that produced no gradient for a slot leaves LAST step's data there for the owner to sum
             self.check_grad_presence([g is not None or getattr(p, "_grad_in_arena", False) for p, g in with_grad])

@@ -547,3 +547,82 @@ def test_debug_check_names_parameters_whose_gradient_exists_on_some_ranks_only()
     for err in run_ranks(_presence_body, 2):
         assert err is not None and "ranks disagree" in err
         assert "b_proj.weight: gradient on data-parallel ranks [0] only" in err
+
+
+class _ExpertBlock(nn.Module):
+    """The optional branch holds dedicated matrices only (like the experts of an
+    MoE layer): nothing of it is left to FSDP2, whose own reduce-scatter needs
+    the same parameters to have gradients on every rank."""
+
+    def __init__(self, d):
+        super().__init__()
+        self.a_proj = nn.Linear(d, d, bias=False)
+        self.b_proj = nn.Linear(d, d, bias=False)
+
+    def forward(self, x, use_b):
+        x = x + torch.tanh(self.a_proj(x))
+        if use_b:
+            x = x + torch.tanh(self.b_proj(x))
+        return x
+
+
+class _ExpertNet(nn.Module):
+    def __init__(self, vocab=64, d=32):
+        super().__init__()
+        self.embed = nn.Embedding(vocab, d)
+        self.layers = nn.ModuleList(_ExpertBlock(d) for _ in range(2))
+        self.head = nn.Linear(d, vocab, bias=False)
+
+    def forward(self, ids, use_b):
+        x = self.embed(ids)
+        for layer in self.layers:
+            x = layer(x, use_b)
+        return F.cross_entropy(self.head(x).flatten(0, 1), ids.flatten())
+
+
+def _zero_fill_body(rank, world, steps):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+    from dmuon_b200.parallel import dgroup
+
+    dgroup.ZERO_FILL_MISSING_GRADS = True      # what DMUON_ZERO_FILL_MISSING_GRADS=1 sets at import
+    mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("dp",))
+    torch.manual_seed(3)
+    model = _ExpertNet()
+    dmuon.dedicate_params(model, mesh, lambda n, p: "proj" in n and p.ndim == 2, reshard_after_forward=False)
+    fully_shard(model, mesh=mesh)              # embedding and head: used on every rank
+    opt = dmuon.Muon(model, lr=0.02, momentum=0.95, weight_decay=0.1, adamw_lr=1e-2, adamw_weight_decay=0.01,
+                     first_step_progress_log=False)
+    for s in range(steps):
+        ids = _sometimes_data(s)[rank * 2 : rank * 2 + 2]
+        opt.zero_grad()
+        model(ids, use_b=(rank == 0)).backward()          # only rank 0 ever runs the optional branch
+        opt.step()
+    return dmuon.get_model_state_dict(model, rank0_only=False)
+
+
+def test_zero_fill_lets_ranks_disagree_about_which_branch_ran():
+    """With ``DMUON_ZERO_FILL_MISSING_GRADS=1`` a dedicated matrix without a
+    gradient on a rank contributes zeros: rank 0 runs the optional branch, rank 1
+    never does, nothing hangs, and all weights follow the single-process run whose
+    loss is the mean of both ranks' losses (the branch's gradient is then half of
+    rank 0's)."""
+    from oracle import muon_adamw_run
+
+    steps = 3
+    torch.manual_seed(3)
+    ref = _ExpertNet()
+
+    def loss_fn(m, s):
+        ids = _sometimes_data(s)
+        return 0.5 * (m(ids[0:2], use_b=True) + m(ids[2:4], use_b=False))
+
+    muon_adamw_run(
+        ref, lambda n, p: "proj" in n and p.ndim == 2, list(range(steps)), loss_fn,
+        lr=0.02, momentum=0.95, weight_decay=0.1, adamw_lr=1e-2, adamw_wd=0.01, betas=(0.9, 0.999), eps=1e-8,
+    )
+    sd = run_ranks(_zero_fill_body, 2, args=(steps,), timeout=120)[0]
+    for n, p in ref.named_parameters():
+        assert (sd[n].float() - p.detach()).abs().max().item() < 5e-4, n

@@ -23,7 +23,7 @@ import torch.distributed as dist
 import torch.nn as nn
 import torch.nn.functional as F
 from torch.distributed.device_mesh import init_device_mesh
-from torch.distributed.fsdp import fully_shard
+from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import dmuon_b200 as dmuon  # noqa: E402
@@ -79,9 +79,11 @@ def main() -> None:
         compute_dtype=torch.bfloat16 if use_cuda else None,   # forward/backward copies; masters stay fp32
         reshard_after_forward=False,                          # keep the published copy for backward ("Z2")
     )
+    # the same compute dtype for what FSDP2 manages, so that activations and dedicated weights agree
+    mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32) if use_cuda else MixedPrecisionPolicy()
     for layer in model.layers:
-        fully_shard(layer, mesh=mesh)
-    fully_shard(model, mesh=mesh)                             # embedding, head, norms: ordinary FSDP2
+        fully_shard(layer, mesh=mesh, mp_policy=mp)
+    fully_shard(model, mesh=mesh, mp_policy=mp)               # embedding, head, norms: ordinary FSDP2
     if rank == 0:
         per_rank = [sum(1 for o in owners.values() if o == r) for r in range(world)]
         print(f"{len(owners)} dedicated matrices, owners per rank: {per_rank}")

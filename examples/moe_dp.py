@@ -20,7 +20,7 @@ import sys
 import torch
 import torch.distributed as dist
 from torch.distributed.device_mesh import init_device_mesh
-from torch.distributed.fsdp import fully_shard
+from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import dmuon_b200 as dmuon  # noqa: E402
@@ -48,9 +48,11 @@ def main() -> None:
     model = MoEModel(cfg).to(device)
     owners = dmuon.dedicate_params(model, mesh, lambda n, p: "proj" in n and p.ndim == 2,
                                    compute_dtype=torch.bfloat16 if use_cuda else None, reshard_after_forward=False)
+    # the same compute dtype for what FSDP2 manages, so that activations and dedicated weights agree
+    mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32) if use_cuda else MixedPrecisionPolicy()
     for layer in model.layers:
-        fully_shard(layer, mesh=mesh)
-    fully_shard(model, mesh=mesh)
+        fully_shard(layer, mesh=mesh, mp_policy=mp)
+    fully_shard(model, mesh=mesh, mp_policy=mp)
     opt = dmuon.Muon(model, lr=0.02, momentum=0.95, weight_decay=0.1, adamw_lr=3e-3, first_step_progress_log=False)
     if rank == 0:
         per_owner = [0] * world

@@ -326,3 +326,34 @@ def test_restored_optimizer_state_takes_the_policy_dtype():
             assert err <= 8e-3 * max(scale, 1e-12), (name, key, err, scale)
             seen += 1
     assert seen >= 28        # every Muon matrix on its owner, plus the AdamW-routed norm weight's two moments
+
+
+def _body_save(rank, world, steps):
+    dmuon, model, opt = _setup(rank, world, "fsdp")
+    _train(rank, world, model, opt, steps)
+    return (dmuon.get_model_state_dict(model, rank0_only=False),
+            dmuon.get_optimizer_state_dict(model, opt, rank0_only=False))
+
+
+def _body_resume_elsewhere(rank, world, mode, msd, osd, start, steps):
+    dmuon, model, opt = _setup(rank, world, mode)
+    dmuon.set_model_state_dict(model, msd)
+    dmuon.set_optimizer_state_dict(model, opt, osd)
+    losses = _train(rank, world, model, opt, steps, start=start)
+    return losses, dmuon.get_model_state_dict(model, rank0_only=False)
+
+
+@pytest.mark.parametrize("mode", ["hsdp", "ddp", "fsdp_gather"])
+def test_checkpoint_written_on_two_ranks_resumes_under_another_placement(mode):
+    """Model and optimizer state saved by a 2-rank FSDP run load into a 4-rank
+    replicate x shard, replicated or all-gather placement (other owners, other
+    shards) and training continues on the single-process trajectory: the
+    checkpoint is a property of the model, not of the topology."""
+    ref_losses, ref_params = oracle_run(4)
+    msd, osd = run_ranks(_body_save, 2, args=(2,))[0]
+    res = run_ranks(_body_resume_elsewhere, 4, args=(mode, msd, osd, 2, 2))
+    losses, sd = res[0]
+    for a, b in zip(losses, ref_losses[2:]):
+        assert abs(a - b) < 2e-4 * max(1.0, abs(b)), (mode, losses, ref_losses)
+    for n, p in ref_params.items():
+        assert (sd[n].float() - p).abs().max().item() < 5e-4, (mode, n)

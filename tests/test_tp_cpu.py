@@ -301,3 +301,70 @@ def test_clipped_tp_gradients_stay_clipped_in_the_step():
     res = run_ranks(_clip_body, 4, timeout=300)
     rel = [v for r in res for v in r]
     assert len(rel) == 6 and max(rel) < 1e-3, rel
+
+
+def _tp_save_body(rank, world, steps):
+    """DP2 x TP2: train, then hand back the full-tensor checkpoint."""
+    import torch.distributed as dist  # noqa: F401
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+    from torch.distributed.tensor.parallel import ColwiseParallel, RowwiseParallel, parallelize_module
+
+    import dmuon_b200 as dmuon
+
+    mesh = init_device_mesh("cpu", (2, 2), mesh_dim_names=("dp", "tp"))
+    torch.manual_seed(0)
+    model = Net()
+    for blk in model.layers:
+        parallelize_module(blk, mesh["tp"], {"up_proj": ColwiseParallel(), "down_proj": RowwiseParallel()})
+    dmuon.dedicate_params(model, mesh["dp"], _pred, reshard_after_forward=False)
+    for blk in model.layers:
+        fully_shard(blk, mesh=mesh["dp"])
+    fully_shard(model, mesh=mesh["dp"])
+    opt = dmuon.Muon(model, lr=LR, momentum=MU, weight_decay=WD, adamw_lr=ALR, first_step_progress_log=False)
+    dp_rank = mesh["dp"].get_local_rank()
+    for s in range(steps):
+        x, y = _data(s)
+        opt.zero_grad()
+        (model(x[dp_rank * 4 : dp_rank * 4 + 4]) - y[dp_rank * 4 : dp_rank * 4 + 4]).pow(2).mean().backward()
+        opt.step()
+    return (dmuon.get_model_state_dict(model, rank0_only=False),
+            dmuon.get_optimizer_state_dict(model, opt, rank0_only=False))
+
+
+def _plain_resume_body(rank, world, msd, osd, start, steps):
+    """Four data-parallel ranks, no tensor parallelism: load the TP run's checkpoint and go on."""
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+
+    mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("dp",))
+    torch.manual_seed(123)                    # other initial weights: everything must come from the checkpoint
+    model = Net()
+    dmuon.dedicate_params(model, mesh, _pred, reshard_after_forward=False)
+    for blk in model.layers:
+        fully_shard(blk, mesh=mesh)
+    fully_shard(model, mesh=mesh)
+    opt = dmuon.Muon(model, lr=LR, momentum=MU, weight_decay=WD, adamw_lr=ALR, first_step_progress_log=False)
+    dmuon.set_model_state_dict(model, msd)
+    dmuon.set_optimizer_state_dict(model, opt, osd)
+    per = 8 // world
+    for s in range(start, start + steps):
+        x, y = _data(s)
+        opt.zero_grad()
+        (model(x[rank * per : (rank + 1) * per]) - y[rank * per : (rank + 1) * per]).pow(2).mean().backward()
+        opt.step()
+    return dmuon.get_model_state_dict(model, rank0_only=False)
+
+
+def test_checkpoint_of_a_tensor_parallel_run_resumes_without_tensor_parallelism():
+    """Momentum of TP matrices is saved as the full matrix (it lives on the TP
+    owner), weights as full tensors: a DP2 x TP2 checkpoint continues on four
+    plain data-parallel ranks along the single-process trajectory."""
+    _, ref_params = _oracle(4)
+    msd, osd = run_ranks(_tp_save_body, 4, args=(2,))[0]
+    assert tuple(osd["dedicated"]["layers.0.up_proj.weight"]["momentum_buffer"].shape) == (64, 32)
+    sd = run_ranks(_plain_resume_body, 4, args=(msd, osd, 2, 2))[0]
+    for n, p in ref_params.items():
+        assert (sd[n].float() - p).abs().max().item() < 2e-4, n

@@ -368,3 +368,67 @@ def test_checkpoint_of_a_tensor_parallel_run_resumes_without_tensor_parallelism(
     sd = run_ranks(_plain_resume_body, 4, args=(msd, osd, 2, 2))[0]
     for n, p in ref_params.items():
         assert (sd[n].float() - p).abs().max().item() < 2e-4, n
+
+
+def _plain_save_body(rank, world, steps):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+
+    mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("dp",))
+    torch.manual_seed(0)
+    model = Net()
+    dmuon.dedicate_params(model, mesh, _pred, reshard_after_forward=False)
+    for blk in model.layers:
+        fully_shard(blk, mesh=mesh)
+    fully_shard(model, mesh=mesh)
+    opt = dmuon.Muon(model, lr=LR, momentum=MU, weight_decay=WD, adamw_lr=ALR, first_step_progress_log=False)
+    per = 8 // world
+    for s in range(steps):
+        x, y = _data(s)
+        opt.zero_grad()
+        (model(x[rank * per : (rank + 1) * per]) - y[rank * per : (rank + 1) * per]).pow(2).mean().backward()
+        opt.step()
+    return (dmuon.get_model_state_dict(model, rank0_only=False),
+            dmuon.get_optimizer_state_dict(model, opt, rank0_only=False))
+
+
+def _tp_resume_body(rank, world, msd, osd, start, steps, gram):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+    from torch.distributed.tensor.parallel import ColwiseParallel, RowwiseParallel, parallelize_module
+
+    import dmuon_b200 as dmuon
+
+    mesh = init_device_mesh("cpu", (2, 2), mesh_dim_names=("dp", "tp"))
+    torch.manual_seed(123)
+    model = Net()
+    for blk in model.layers:
+        parallelize_module(blk, mesh["tp"], {"up_proj": ColwiseParallel(), "down_proj": RowwiseParallel()})
+    dmuon.dedicate_params(model, mesh["dp"], _pred, reshard_after_forward=False)
+    for blk in model.layers:
+        fully_shard(blk, mesh=mesh["dp"])
+    fully_shard(model, mesh=mesh["dp"])
+    extra = dict(tp_distributed_gram=True, tp_distributed_gram_policy="all") if gram else {}
+    opt = dmuon.Muon(model, lr=LR, momentum=MU, weight_decay=WD, adamw_lr=ALR, first_step_progress_log=False, **extra)
+    dmuon.set_model_state_dict(model, msd)
+    dmuon.set_optimizer_state_dict(model, opt, osd)
+    dp_rank = mesh["dp"].get_local_rank()
+    for s in range(start, start + steps):
+        x, y = _data(s)
+        opt.zero_grad()
+        (model(x[dp_rank * 4 : dp_rank * 4 + 4]) - y[dp_rank * 4 : dp_rank * 4 + 4]).pow(2).mean().backward()
+        opt.step()
+    return dmuon.get_model_state_dict(model, rank0_only=False)
+
+
+@pytest.mark.parametrize("gram", [False, True])
+def test_plain_checkpoint_resumes_under_tensor_parallelism(gram):
+    """The other direction: full momentum matrices land on the TP owners (and,
+    for the Gram-factor route, their slices on every TP rank)."""
+    _, ref_params = _oracle(4)
+    msd, osd = run_ranks(_plain_save_body, 4, args=(2,))[0]
+    sd = run_ranks(_tp_resume_body, 4, args=(msd, osd, 2, 2, gram))[0]
+    for n, p in ref_params.items():
+        assert (sd[n].float() - p).abs().max().item() < 2e-4, (gram, n)

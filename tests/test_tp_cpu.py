@@ -328,6 +328,14 @@ def _tp_save_body(rank, world, steps):
         opt.zero_grad()
         (model(x[dp_rank * 4 : dp_rank * 4 + 4]) - y[dp_rank * 4 : dp_rank * 4 + 4]).pow(2).mean().backward()
         opt.step()
+    # the summaries also describe tensor-parallel set-ups (and stay JSON-friendly)
+    import json
+
+    plan = dmuon.summarize_comm_plan(model)
+    rows = dmuon.summarize_param_groups(model, opt)["parameters"]
+    json.dumps(plan), json.dumps(rows)
+    assert plan["groups"][0]["tp_param_count"] == 2 and all(r["is_dtensor"] for r in rows if "proj" in r["name"])
+    assert all(c["tp_owner_local_rank"] in (0, 1) for c in plan["groups"][0]["param_collectives"])
     return (dmuon.get_model_state_dict(model, rank0_only=False),
             dmuon.get_optimizer_state_dict(model, opt, rank0_only=False))
 

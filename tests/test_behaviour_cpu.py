@@ -626,3 +626,49 @@ def test_zero_fill_lets_ranks_disagree_about_which_branch_ran():
     sd = run_ranks(_zero_fill_body, 2, args=(steps,), timeout=120)[0]
     for n, p in ref.named_parameters():
         assert (sd[n].float() - p.detach()).abs().max().item() < 5e-4, n
+
+
+def _eval_between_body(rank, world, reshard):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+    from test_e2e_cpu import HP, _build_model, _data, _pred
+
+    mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("dp",))
+    model = _build_model()
+    dmuon.dedicate_params(model, mesh, _pred, reshard_after_forward=reshard)
+    for layer in model.layers:
+        fully_shard(layer, mesh=mesh, reshard_after_forward=reshard)
+    fully_shard(model, mesh=mesh, reshard_after_forward=reshard)
+    opt = dmuon.Muon(model, lr=HP["lr"], ns_steps=5, adamw_lr=HP["adamw_lr"], weight_decay=HP["weight_decay"],
+                     momentum=HP["momentum"], adamw_weight_decay=HP["adamw_wd"], first_step_progress_log=False)
+    per = 4 // world
+    evals = []
+    for s in range(3):
+        x, y = _data(s)
+        x, y = x[rank * per : (rank + 1) * per], y[rank * per : (rank + 1) * per]
+        opt.zero_grad()
+        model(x, labels=y).backward()
+        opt.step()
+        # evaluation between steps: forwards without a backward, in eval mode and under no_grad, twice
+        model.eval()
+        with torch.no_grad():
+            evals.append([float(model(x, labels=y)) for _ in range(2)])
+        model.train()
+    return dmuon.get_model_state_dict(model, rank0_only=False), evals
+
+
+@pytest.mark.parametrize("reshard", [False, True])
+def test_evaluation_forwards_between_steps_do_not_disturb_training(reshard):
+    """Forward-only passes (``eval()`` + ``no_grad``) between optimizer steps see
+    the freshly updated weights (both passes give the same loss) and leave the
+    trajectory on the single-process one, with the published copies kept (Z2) or
+    dropped (Z3) after forward."""
+    from test_e2e_cpu import oracle_run
+
+    _, ref_params = oracle_run(3)
+    for sd, evals in run_ranks(_eval_between_body, 2, args=(reshard,)):
+        assert all(abs(a - b) < 1e-6 for a, b in evals), evals
+        for n, p in ref_params.items():
+            assert (sd[n].float() - p).abs().max().item() < 5e-4, (reshard, n)

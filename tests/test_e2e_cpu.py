@@ -99,3 +99,48 @@ def test_single_rank_world():
     assert n_owned == 28 and owners == [0]
     for a, b in zip(losses, ref_losses):
         assert abs(a - b) < 1e-4
+
+
+def _variant_body(rank, world, nesterov, backend, steps):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import dmuon_b200 as dmuon
+
+    mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("dp",))
+    model = _build_model()
+    dmuon.dedicate_params(model, mesh, _pred, reshard_after_forward=False)
+    for layer in model.layers:
+        fully_shard(layer, mesh=mesh)
+    fully_shard(model, mesh=mesh)
+    opt = dmuon.Muon(
+        model, lr=HP["lr"], ns_steps=5, adamw_lr=HP["adamw_lr"], weight_decay=HP["weight_decay"], momentum=HP["momentum"],
+        adamw_weight_decay=HP["adamw_wd"], nesterov=nesterov, ns_backend=backend, first_step_progress_log=False,
+    )
+    per = 4 // world
+    for s in range(steps):
+        x, y = _data(s)
+        opt.zero_grad()
+        model(x[rank * per : (rank + 1) * per], labels=y[rank * per : (rank + 1) * per]).backward()
+        opt.step()
+    return dmuon.get_model_state_dict(model, rank0_only=False)
+
+
+@pytest.mark.parametrize("nesterov,backend", [(False, "gram"), (True, "direct"), (False, "direct")])
+def test_plain_momentum_and_the_direct_formulation_follow_the_oracle(nesterov, backend):
+    """``nesterov=False`` feeds the momentum buffer itself to Newton-Schulz; the
+    direct formulation iterates on the matrix instead of its Gram matrix.  Both
+    must land on the single-process trajectory (the oracle's iteration IS the
+    direct one, in float64, with the same coefficients)."""
+    from oracle import muon_adamw_run
+
+    steps = 4
+    ref = _build_model()
+    muon_adamw_run(
+        ref, _pred, [_data(s) for s in range(steps)], lambda m, b: m(b[0], labels=b[1]),
+        lr=HP["lr"], momentum=HP["momentum"], weight_decay=HP["weight_decay"], adamw_lr=HP["adamw_lr"],
+        adamw_wd=HP["adamw_wd"], betas=HP["betas"], eps=HP["eps"], nesterov=nesterov,
+    )
+    sd = run_ranks(_variant_body, 2, args=(nesterov, backend, steps))[0]
+    for n, p in ref.named_parameters():
+        assert (sd[n].float() - p.detach()).abs().max().item() < 5e-4, (nesterov, backend, n)

@@ -67,12 +67,16 @@ def test_ownership_benchmark_arms_follow_the_same_trajectory():
     orthogonalising the all-gathered gradient (no ownership, nothing of this
     package's placement code) and dedicated ownership must reach the same loss --
     an end-to-end oracle that shares only the model and the Newton-Schulz function."""
+    import socket
     import subprocess
     import sys
 
+    with socket.socket() as sock:                     # a port nobody holds right now
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
     cmd = [
         sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
-        "--master-port", "29641", str(ROOT / "benchmarks" / "bench_e2e.py"), "--cpu", "--arms", "redundant,owned",
+        "--master-port", str(port), str(ROOT / "benchmarks" / "bench_e2e.py"), "--cpu", "--arms", "redundant,owned",
         "--layers", "2", "--width", "128", "--heads", "4", "--vocab", "512", "--batch", "2", "--seq", "64",
         "--steps", "3", "--warmup", "1",
     ]
